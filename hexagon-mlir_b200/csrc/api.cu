@@ -1,0 +1,328 @@
+// Host-side runtime of libhexb200: status strings, error text, option store, device cache, and the
+// `_host` launcher entry points that stage tensors across the host/device boundary.
+//
+// The `_host` entry points take the place of the wrapper main() the reference generates per kernel
+// (qcom_hexagon_backend/backend/triton_hexagon_launcher.py:111-123): that program loads the input
+// tensors from files pushed over adb, runs the kernel and dumps the outputs for the host to pull
+// back; here the crossing is a pair of PCIe copies around an in-process launch.
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+
+#include "common.cuh"
+
+namespace hexb {
+
+static thread_local char g_err_text[256] = "";
+
+void set_cuda_error(cudaError_t e, const char *where) {
+  snprintf(g_err_text, sizeof(g_err_text), "%s: %s (%s)", where, cudaGetErrorName(e),
+           cudaGetErrorString(e));
+}
+
+int check_launch(const char *where) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_cuda_error(e, where);
+    return HEXB_ERR_CUDA;
+  }
+  return HEXB_OK;
+}
+
+static std::mutex g_mu;
+static std::map<std::string, int> &options() {
+  static std::map<std::string, int> m;
+  return m;
+}
+
+int option(const char *key, int dflt) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = options().find(key);
+  return it == options().end() ? dflt : it->second;
+}
+
+static const char *kKnownOptions[] = {
+    "softmax_vpt_max", "softmax_force_stream", "norm_vpt_max", "norm_force_stream",
+    "norm_ctas_per_sm", "gemm_bn", "gemm_b_lbo", "gemm_b_sbo", "gemm_force_simt", "attn_force_simt",
+    "attn_v_lbo", "attn_v_sbo",
+    "host_chunks", nullptr};
+
+int current_device(DeviceInfo *out) {
+  static DeviceInfo cache[64];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return HEXB_ERR_NO_DEVICE;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceInfo &d = cache[dev];
+  if (d.device != dev) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+      cudaGetLastError();
+      return HEXB_ERR_NO_DEVICE;
+    }
+    d.sm_count = v;
+    cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    d.smem_optin = (size_t)v;
+    d.device = dev;
+  }
+  *out = d;
+  if (d.cc_major != 10) return HEXB_ERR_NO_DEVICE;  // the binary holds sm_100a code only
+  return HEXB_OK;
+}
+
+// ---- per-device staging memory for the `_host` entry points (grow-only, released on request).
+struct Staging {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+  cudaStream_t streams[3] = {nullptr, nullptr, nullptr};
+  cudaEvent_t events[8] = {};
+  bool ready = false;
+};
+static Staging g_staging[64];
+static std::mutex g_staging_mu;
+
+static int staging_get(size_t bytes, Staging **out) {
+  int dev = -1;
+  HEXB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return HEXB_ERR_NO_DEVICE;
+  Staging &s = g_staging[dev];
+  if (!s.ready) {
+    for (auto &st : s.streams) HEXB_CUDA_OK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    for (auto &ev : s.events) HEXB_CUDA_OK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    s.ready = true;
+  }
+  if (s.bytes < bytes) {
+    if (s.ptr) HEXB_CUDA_OK(cudaFree(s.ptr));
+    s.ptr = nullptr;
+    s.bytes = 0;
+    HEXB_CUDA_OK(cudaMalloc(&s.ptr, bytes));
+    s.bytes = bytes;
+  }
+  *out = &s;
+  return HEXB_OK;
+}
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static inline size_t dt_size(int dt) { return dt == HEXB_DT_F16 ? 2 : dt == HEXB_DT_F32 ? 4 : 0; }
+
+// Row-wise operators: the rows are cut into chunks that run as H2D copy -> kernel -> D2H copy on
+// rotating streams, so that the upload of chunk i+1, the kernel of chunk i and the download of
+// chunk i-1 overlap (PCIe is full duplex).  `launch(x_dev, y_dev, row0, nrows, stream)`.
+template <typename F>
+static int rows_pipeline(const void *x, void *y, int64_t rows, int64_t cols, size_t esz,
+                         size_t extra_bytes, F &&launch_with_extra) {
+  if (rows < 0 || cols < 0) return HEXB_ERR_BAD_ARG;
+  if (rows == 0 || cols == 0) return HEXB_OK;
+  if (!x || !y) return HEXB_ERR_BAD_ARG;
+  const size_t row_bytes = (size_t)cols * esz;
+  const size_t mat = align_up((size_t)rows * row_bytes, 256);
+  const size_t extra = align_up(extra_bytes, 256);
+  Staging *s = nullptr;
+  if (int st = staging_get(2 * mat + extra, &s)) return st;
+  char *dx = (char *)s->ptr, *dy = dx + mat, *de = dy + mat;
+  int chunks = option("host_chunks", 8);
+  if (chunks < 1) chunks = 1;
+  if ((int64_t)chunks > rows) chunks = (int)rows;
+  if ((size_t)rows * row_bytes < ((size_t)4 << 20)) chunks = 1;
+  if (int st = launch_with_extra(nullptr, nullptr, de, 0, 0, s->streams[0])) return st;  // uploads extras
+  HEXB_CUDA_OK(cudaEventRecord(s->events[0], s->streams[0]));
+  for (int i = 1; i < 3; ++i) HEXB_CUDA_OK(cudaStreamWaitEvent(s->streams[i], s->events[0], 0));
+  const int64_t per = (rows + chunks - 1) / chunks;
+  for (int c = 0; c < chunks; ++c) {
+    const int64_t r0 = (int64_t)c * per;
+    const int64_t nr = rows - r0 < per ? rows - r0 : per;
+    if (nr <= 0) break;
+    cudaStream_t st = s->streams[c % 3];
+    const size_t off = (size_t)r0 * row_bytes;
+    HEXB_CUDA_OK(cudaMemcpyAsync(dx + off, (const char *)x + off, (size_t)nr * row_bytes,
+                                 cudaMemcpyHostToDevice, st));
+    if (int e = launch_with_extra(dx + off, dy + off, de, r0, nr, st)) return e;
+    HEXB_CUDA_OK(cudaMemcpyAsync((char *)y + off, dy + off, (size_t)nr * row_bytes,
+                                 cudaMemcpyDeviceToHost, st));
+  }
+  for (auto &st : s->streams) HEXB_CUDA_OK(cudaStreamSynchronize(st));
+  return HEXB_OK;
+}
+
+}  // namespace hexb
+
+using namespace hexb;
+
+extern "C" int hexb_version(void) { return 100; }
+
+extern "C" const char *hexb_status_string(int s) {
+  switch (s) {
+    case HEXB_OK: return "HEXB_OK";
+    case HEXB_ERR_BAD_ARG: return "HEXB_ERR_BAD_ARG";
+    case HEXB_ERR_UNSUPPORTED: return "HEXB_ERR_UNSUPPORTED";
+    case HEXB_ERR_MISALIGNED: return "HEXB_ERR_MISALIGNED";
+    case HEXB_ERR_CUDA: return "HEXB_ERR_CUDA";
+    case HEXB_ERR_TIMEOUT: return "HEXB_ERR_TIMEOUT";
+    case HEXB_ERR_WORKSPACE: return "HEXB_ERR_WORKSPACE";
+    case HEXB_ERR_NO_DEVICE: return "HEXB_ERR_NO_DEVICE";
+    default: return "HEXB_ERR_UNKNOWN";
+  }
+}
+
+extern "C" const char *hexb_last_cuda_error(void) { return g_err_text; }
+
+extern "C" int hexb_set_option(const char *key, int value) {
+  if (!key) return HEXB_ERR_BAD_ARG;
+  for (const char **k = kKnownOptions; *k; ++k)
+    if (!strcmp(*k, key)) {
+      std::lock_guard<std::mutex> lk(g_mu);
+      options()[key] = value;
+      return HEXB_OK;
+    }
+  return HEXB_ERR_BAD_ARG;
+}
+
+extern "C" int hexb_get_option(const char *key, int *value) {
+  if (!key || !value) return HEXB_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = options().find(key);
+  if (it == options().end()) return HEXB_ERR_BAD_ARG;
+  *value = it->second;
+  return HEXB_OK;
+}
+
+extern "C" int hexb_host_staging_release(void) {
+  int dev = -1;
+  HEXB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return HEXB_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lk(g_staging_mu);
+  Staging &s = g_staging[dev];
+  if (s.ptr) HEXB_CUDA_OK(cudaFree(s.ptr));
+  s.ptr = nullptr;
+  s.bytes = 0;
+  return HEXB_OK;
+}
+
+extern "C" int hexb_softmax_host(int dtype, const void *x, void *y, int64_t rows, int64_t cols) {
+  const size_t esz = dt_size(dtype);
+  if (!esz) return HEXB_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lk(g_staging_mu);
+  return rows_pipeline(x, y, rows, cols, esz, 0,
+                       [&](void *dx, void *dy, void *, int64_t, int64_t nr, cudaStream_t st) -> int {
+                         if (!dx) return HEXB_OK;
+                         return dtype == HEXB_DT_F16
+                                    ? hexb_softmax_f16(dx, dy, nr, cols, cols, cols, st)
+                                    : hexb_softmax_f32((const float *)dx, (float *)dy, nr, cols, cols, cols, st);
+                       });
+}
+
+extern "C" int hexb_layer_norm_host(int dtype, const void *x, void *y, const void *w, const void *b,
+                                    float *mean, float *rstd, int64_t rows, int64_t cols, float eps) {
+  const size_t esz = dt_size(dtype);
+  if (!esz) return HEXB_ERR_UNSUPPORTED;
+  if (rows > 0 && cols > 0 && (!w || !b)) return HEXB_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lk(g_staging_mu);
+  const size_t vb = align_up((size_t)cols * esz, 256);
+  const size_t sb = align_up((size_t)rows * 4, 256);
+  int st = rows_pipeline(
+      x, y, rows, cols, esz, 2 * vb + 2 * sb,
+      [&](void *dx, void *dy, void *de, int64_t r0, int64_t nr, cudaStream_t s) -> int {
+        char *dw = (char *)de, *db = dw + vb;
+        float *dm = (float *)(db + vb), *dr = (float *)((char *)dm + sb);
+        if (!dx) {
+          HEXB_CUDA_OK(cudaMemcpyAsync(dw, w, (size_t)cols * esz, cudaMemcpyHostToDevice, s));
+          HEXB_CUDA_OK(cudaMemcpyAsync(db, b, (size_t)cols * esz, cudaMemcpyHostToDevice, s));
+          return HEXB_OK;
+        }
+        int e = dtype == HEXB_DT_F16
+                    ? hexb_layer_norm_f16(dx, dy, dw, db, dm + r0, dr + r0, nr, cols, cols, cols, eps, s)
+                    : hexb_layer_norm_f32((const float *)dx, (float *)dy, (const float *)dw,
+                                          (const float *)db, dm + r0, dr + r0, nr, cols, cols, cols, eps, s);
+        if (e) return e;
+        if (mean) HEXB_CUDA_OK(cudaMemcpyAsync(mean + r0, dm + r0, (size_t)nr * 4, cudaMemcpyDeviceToHost, s));
+        if (rstd) HEXB_CUDA_OK(cudaMemcpyAsync(rstd + r0, dr + r0, (size_t)nr * 4, cudaMemcpyDeviceToHost, s));
+        return HEXB_OK;
+      });
+  return st;
+}
+
+extern "C" int hexb_rms_norm_host(int dtype, const void *x, void *y, const void *w, int64_t rows,
+                                  int64_t cols, float eps) {
+  const size_t esz = dt_size(dtype);
+  if (!esz) return HEXB_ERR_UNSUPPORTED;
+  if (rows > 0 && cols > 0 && !w) return HEXB_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lk(g_staging_mu);
+  const size_t vb = align_up((size_t)cols * esz, 256);
+  return rows_pipeline(
+      x, y, rows, cols, esz, vb,
+      [&](void *dx, void *dy, void *de, int64_t, int64_t nr, cudaStream_t s) -> int {
+        if (!dx) {
+          HEXB_CUDA_OK(cudaMemcpyAsync(de, w, (size_t)cols * esz, cudaMemcpyHostToDevice, s));
+          return HEXB_OK;
+        }
+        return dtype == HEXB_DT_F16
+                   ? hexb_rms_norm_f16(dx, dy, de, nr, cols, cols, cols, eps, s)
+                   : hexb_rms_norm_f32((const float *)dx, (float *)dy, (const float *)de, nr, cols, cols, cols, eps, s);
+      });
+}
+
+extern "C" int hexb_matmul_f16_host(const void *A, const void *B, void *C, int64_t M, int64_t N,
+                                    int64_t K, int out_dtype) {
+  if (M < 0 || N < 0 || K < 0) return HEXB_ERR_BAD_ARG;
+  const size_t osz = dt_size(out_dtype);
+  if (!osz) return HEXB_ERR_UNSUPPORTED;
+  if (M == 0 || N == 0) return HEXB_OK;
+  if (!A || !B || !C) return HEXB_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lk(g_staging_mu);
+  const size_t ab = align_up((size_t)M * K * 2, 256), bb = align_up((size_t)K * N * 2, 256);
+  const size_t cb = align_up((size_t)M * N * osz, 256);
+  Staging *s = nullptr;
+  if (int st = staging_get(ab + bb + cb, &s)) return st;
+  char *dA = (char *)s->ptr, *dB = dA + ab, *dC = dB + bb;
+  cudaStream_t st = s->streams[0];
+  if (K > 0) {
+    HEXB_CUDA_OK(cudaMemcpyAsync(dA, A, (size_t)M * K * 2, cudaMemcpyHostToDevice, st));
+    HEXB_CUDA_OK(cudaMemcpyAsync(dB, B, (size_t)K * N * 2, cudaMemcpyHostToDevice, st));
+  }
+  if (int e = hexb_matmul_f16(dA, dB, dC, nullptr, M, N, K, K, N, N, out_dtype, st)) return e;
+  HEXB_CUDA_OK(cudaMemcpyAsync(C, dC, (size_t)M * N * osz, cudaMemcpyDeviceToHost, st));
+  HEXB_CUDA_OK(cudaStreamSynchronize(st));
+  return HEXB_OK;
+}
+
+extern "C" int hexb_attention_fwd_host(int dtype, const void *Q, const void *K, const void *V,
+                                       void *Out, int64_t Z, int64_t H, int64_t N_CTX, int64_t D,
+                                       float sm_scale, int causal) {
+  const size_t esz = dt_size(dtype);
+  if (!esz) return HEXB_ERR_UNSUPPORTED;
+  if (Z < 0 || H < 0 || N_CTX < 0 || D < 0) return HEXB_ERR_BAD_ARG;
+  if (Z == 0 || H == 0 || N_CTX == 0 || D == 0) return HEXB_OK;
+  if (!Q || !K || !V || !Out) return HEXB_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lk(g_staging_mu);
+  // One pipeline stage per batch index: upload Q/K/V of batch z, run its heads, download O.
+  const size_t per_z = (size_t)H * N_CTX * D * esz;
+  const size_t tb = align_up((size_t)Z * per_z, 256);
+  Staging *s = nullptr;
+  if (int st = staging_get(4 * tb, &s)) return st;
+  char *dq = (char *)s->ptr, *dk = dq + tb, *dv = dk + tb, *dout = dv + tb;
+  const int64_t sz = H * N_CTX * D, sh = N_CTX * D, sn = D;
+  const int64_t strides[12] = {sz, sh, sn, sz, sh, sn, sz, sh, sn, sz, sh, sn};
+  for (int64_t z = 0; z < Z; ++z) {
+    cudaStream_t st = s->streams[z % 3];
+    const size_t off = (size_t)z * per_z;
+    HEXB_CUDA_OK(cudaMemcpyAsync(dq + off, (const char *)Q + off, per_z, cudaMemcpyHostToDevice, st));
+    HEXB_CUDA_OK(cudaMemcpyAsync(dk + off, (const char *)K + off, per_z, cudaMemcpyHostToDevice, st));
+    HEXB_CUDA_OK(cudaMemcpyAsync(dv + off, (const char *)V + off, per_z, cudaMemcpyHostToDevice, st));
+    int e = dtype == HEXB_DT_F16
+                ? hexb_attention_fwd_f16(dq + off, dk + off, dv + off, dout + off, 1, H, N_CTX, D,
+                                         strides, sm_scale, causal, st)
+                : hexb_attention_fwd_f32((const float *)(dq + off), (const float *)(dk + off),
+                                         (const float *)(dv + off), (float *)(dout + off), 1, H,
+                                         N_CTX, D, strides, sm_scale, causal, st);
+    if (e) return e;
+    HEXB_CUDA_OK(cudaMemcpyAsync((char *)Out + off, dout + off, per_z, cudaMemcpyDeviceToHost, st));
+  }
+  for (auto &st : s->streams) HEXB_CUDA_OK(cudaStreamSynchronize(st));
+  return HEXB_OK;
+}

@@ -1,0 +1,476 @@
+// Flash-attention forward on the Blackwell tensor cores (tcgen05 + TMEM + TMA), fp16 in/out.
+//
+// Reference semantics: attention_fwd_kernel + _attn_fwd_inner
+// (test/python/triton/test_flash_attention.py:37-168) and the fp16 MLIR form
+// (test/python/mlir/hexkl_attention/input.mlir:5-168) of qualcomm/hexagon-mlir: per block of query
+// rows, loop over key/value blocks; qk = Q.K^T; base-2 online softmax with the scale folded in
+// (qk_scale = sm_scale * 1.44269504); acc = acc*alpha + P.V with P truncated to fp16 before the
+// second product; epilogue acc / l.  The causal flag adds the -inf mask above the diagonal that
+// tm_tensor.attention takes as an additive mask (lib/Transforms/LowerTmTensor.cpp:70-235).
+//
+// One CTA = one 128-row query tile of one (batch, head); 192 threads:
+//   warp 0      TMA producer (Q once; K_j, V_j per step; single buffers, refilled as soon as the
+//               MMA that read them has completed);
+//   warp 1      MMA issuer: S = Q.K_j^T (8 x tcgen05.mma 128x128x16, operands in smem), then
+//               O += P_j.V_j (P read from TMEM, V consumed as stored = "MN-major" operand);
+//   warps 2..5  one query row per thread: tcgen05.ld S, row max, P = exp2(S*scale - m) written back
+//               to TMEM as fp16 over the S columns, running sum; O is rescaled in TMEM only when a
+//               row max grows by more than 2^8 (the same reference max is used for P and l, so the
+//               final O/l is exact); epilogue O/l -> fp16 -> global.
+// Two CTAs share an SM (96 KiB smem and 256 TMEM columns each), so one CTA's softmax overlaps the
+// other's MMAs.  Every mbarrier wait is bounded.
+//
+// A CUDA-core kernel covers fp32 tensors (the dtype of the reference's Triton test) and head
+// sizes / strides the TMA path cannot take.
+#include "tc_sm100.cuh"
+
+namespace hexb {
+
+static __device__ int g_attn_status = 0;
+
+namespace attn {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_N = 128;
+constexpr int THREADS = 192;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+template <int HD>
+struct Cfg {
+  static constexpr int CHUNKS = HD / 64;             // 64-column (128-byte) swizzle chunks
+  static constexpr int TILE_BYTES = 128 * HD * 2;    // Q, K or V tile
+  static constexpr int CHUNK_BYTES = 128 * 128;      // 128 rows x 128 bytes
+  static constexpr int BAR_BYTES = 8 * 8 + 16;
+  static constexpr int NEEDED = 3 * TILE_BYTES + BAR_BYTES + 1024;
+  static constexpr int SMEM_BYTES = NEEDED < 100 * 1024 ? 100 * 1024 : NEEDED;  // caps residency at 2 CTAs/SM
+  static constexpr int TMEM_COLS = 256;              // S: [0,128)  (P aliases [0,64));  O: [128,128+HD)
+  static constexpr int O_COL = 128;
+};
+
+struct Params {
+  __half *out;
+  int64_t so_z, so_h, so_n;
+  int Z, H, N_CTX;
+  int num_q_tiles;
+  float scale_log2;
+  int causal;
+  int out_vec_ok;
+  uint32_t v_lbo, v_sbo;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 2)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const Params p) {
+  using cfg = Cfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = tc::smem_u32(smem_raw);
+  const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+  uint8_t *smem = smem_raw + pad;
+  const uint32_t smem_addr = raw_addr + pad;
+  const uint32_t sQ = smem_addr, sK = sQ + cfg::TILE_BYTES, sV = sK + cfg::TILE_BYTES;
+  const uint32_t bar0 = sV + cfg::TILE_BYTES;
+  const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = bar0 + 16, v_full = bar0 + 24,
+                 v_empty = bar0 + 32, s_full = bar0 + 40, p_full = bar0 + 48, o_full = bar0 + 56;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 3 * cfg::TILE_BYTES + 64);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // work item: heavy (late) query tiles first when causal
+  const int bh_count = p.Z * p.H;
+  const int q_rank = blockIdx.x / bh_count;
+  const int bh = blockIdx.x - q_rank * bh_count;
+  const int z = bh / p.H, h = bh - z * p.H;
+  const int q_tile = p.causal ? p.num_q_tiles - 1 - q_rank : q_rank;
+  const int m0 = q_tile * BLOCK_M;
+  int n_kv = (p.N_CTX + BLOCK_N - 1) / BLOCK_N;
+  if (p.causal && q_tile + 1 < n_kv) n_kv = q_tile + 1;
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(q_full, 1);
+    tc::mbar_init(k_full, 1);
+    tc::mbar_init(k_empty, 1);
+    tc::mbar_init(v_full, 1);
+    tc::mbar_init(v_empty, 1);
+    tc::mbar_init(s_full, 1);
+    tc::mbar_init(p_full, 4);
+    tc::mbar_init(o_full, 1);
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::prefetch_tensormap(&tmQ);
+    tc::prefetch_tensormap(&tmK);
+    tc::prefetch_tensormap(&tmV);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tc::smem_u32(tmem_slot), cfg::TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tP = tmem_base, tO = tmem_base + cfg::O_COL;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tc::mbar_arrive_expect_tx(q_full, cfg::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < cfg::CHUNKS; ++c)
+        tc::tma_load_4d(sQ + c * cfg::CHUNK_BYTES, &tmQ, c * 64, m0, h, z, q_full);
+      for (int j = 0; j < n_kv; ++j) {
+        const uint32_t ph = (uint32_t)j & 1u;
+        if (!tc::mbar_wait(k_empty, ph ^ 1u, abort_flag)) break;
+        tc::mbar_arrive_expect_tx(k_full, cfg::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < cfg::CHUNKS; ++c)
+          tc::tma_load_4d(sK + c * cfg::CHUNK_BYTES, &tmK, c * 64, j * BLOCK_N, h, z, k_full);
+        if (!tc::mbar_wait(v_empty, ph ^ 1u, abort_flag)) break;
+        tc::mbar_arrive_expect_tx(v_full, cfg::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < cfg::CHUNKS; ++c)
+          tc::tma_load_4d(sV + c * cfg::CHUNK_BYTES, &tmV, c * 64, j * BLOCK_N, h, z, v_full);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = tc::make_idesc_f16_f32(BLOCK_M, BLOCK_N, 0, 0);
+      constexpr uint32_t idesc_pv = tc::make_idesc_f16_f32(BLOCK_M, HD, 0, 1);
+      bool ok = tc::mbar_wait(q_full, 0, abort_flag);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const uint32_t ph = (uint32_t)j & 1u;
+        if (!tc::mbar_wait(k_full, ph, abort_flag)) break;
+        tc::tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (uint32_t)((k >> 2) * cfg::CHUNK_BYTES + (k & 3) * 32);
+          tc::mma_f16_ss(tS, tc::make_smem_desc_sw128(sQ + off, 16, 1024),
+                         tc::make_smem_desc_sw128(sK + off, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
+        }
+        tc::mma_commit(s_full);
+        tc::mma_commit(k_empty);
+        if (!tc::mbar_wait(p_full, ph, abort_flag)) break;
+        if (!tc::mbar_wait(v_full, ph, abort_flag)) break;
+        tc::tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BLOCK_N / 16; ++k) {
+          // A = P rows from TMEM (16 fp16 = 8 columns per step); B = V: 16 kv rows = 2 swizzle atoms.
+          tc::mma_f16_ts(tO, tP + (uint32_t)(k * 8),
+                         tc::make_smem_desc_sw128(sV + (uint32_t)(k * 2048), p.v_lbo, p.v_sbo),
+                         idesc_pv, (j | k) != 0 ? 1u : 0u);
+        }
+        tc::mma_commit(v_empty);
+        if (j == n_kv - 1) tc::mma_commit(o_full);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax / correction / epilogue
+    const int q = warp & 3;
+    const int r = q * 32 + lane;       // row inside the tile == TMEM lane
+    const int qi = m0 + r;             // query index
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!tc::mbar_wait(s_full, (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
+      tc::tc_fence_after();
+      const int kv0 = j * BLOCK_N;
+      const bool need_mask = (p.causal && kv0 + BLOCK_N - 1 > m0) || (kv0 + BLOCK_N > p.N_CTX);
+      // pass 1: row maximum of the scaled scores
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t v[32];
+        tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c * 32), v);
+        tc::tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int kv = kv0 + c * 32 + e;
+            const bool dead = (p.causal && kv > qi) || kv >= p.N_CTX;
+            mx = fmaxf(mx, dead ? -INFINITY : __uint_as_float(v[e]));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        }
+      }
+      mx *= p.scale_log2;  // scale > 0: max commutes with the scaling
+      const float m_new = fmaxf(m_ref, mx);
+      if (j == 0) {
+        m_ref = m_new;
+      } else if (__any_sync(0xffffffffu, m_new - m_ref > kRescaleThreshold)) {
+        // S_j complete implies P_{j-1}.V_{j-1} complete (MMAs retire in issue order): O is quiescent.
+        const float alpha = exp2f(m_ref - m_new);
+        m_ref = m_new;
+        l *= alpha;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tc::tmem_st_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+        }
+      }
+      // pass 2: P = exp2(S*scale - m_ref) as fp16 over the S columns, running row sum
+      const float neg_m = -m_ref;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t v[32];
+        tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c * 32), v);
+        tc::tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0 = exp2f(fmaf(__uint_as_float(v[e]), p.scale_log2, neg_m));
+          float p1 = exp2f(fmaf(__uint_as_float(v[e + 1]), p.scale_log2, neg_m));
+          if (need_mask) {
+            const int kv = kv0 + c * 32 + e;
+            if ((p.causal && kv > qi) || kv >= p.N_CTX) p0 = 0.f;
+            if ((p.causal && kv + 1 > qi) || kv + 1 >= p.N_CTX) p1 = 0.f;
+          }
+          const __half2 hp = __floats2half2_rn(p0, p1);
+          // the sum uses the rounded values the second product will see
+          const float2 back = __half22float2(hp);
+          l += back.x + back.y;
+          pk[e >> 1] = *reinterpret_cast<const uint32_t *>(&hp);
+        }
+        tc::tmem_st_32x16(tP + lane_off + (uint32_t)(c * 16), pk);
+      }
+      tc::tmem_st_wait();
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(p_full);
+    }
+    if (ok && tc::mbar_wait(o_full, 0, abort_flag)) {
+      tc::tc_fence_after();
+      const float inv = 1.0f / l;
+      __half *orow = p.out + (int64_t)z * p.so_z + (int64_t)h * p.so_h + (int64_t)qi * p.so_n;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+        tc::tmem_ld_wait();
+        if (qi < p.N_CTX) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[g * 8 + e]) * inv;
+            if (p.out_vec_ok) {
+              Vec16<__half> ov;
+              ov.pack(f);
+              *reinterpret_cast<uint4 *>(orow + c * 32 + g * 8) = ov.raw;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) orow[c * 32 + g * 8 + e] = __float2half_rn(f[e]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, cfg::TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_attn_status, (int)HEXB_ERR_TIMEOUT);
+}
+
+// CUDA-core forward for fp32 tensors and for shapes the TMA path cannot take: one warp per query
+// row, 32 keys per step (one per lane), base-2 online softmax exactly as _attn_fwd_inner writes it
+// (running max of scaled scores, alpha = exp2(m_old - m_new)); each lane owns D/32 output columns.
+template <typename T, int MAXD>
+__global__ void __launch_bounds__(128)
+attn_fwd_simt_kernel(const T *__restrict__ Q, const T *__restrict__ K, const T *__restrict__ V,
+                     T *__restrict__ O, int Z, int H, int N_CTX, int D, const int64_t sq_z,
+                     const int64_t sq_h, const int64_t sq_n, const int64_t sk_z, const int64_t sk_h,
+                     const int64_t sk_n, const int64_t sv_z, const int64_t sv_h, const int64_t sv_n,
+                     const int64_t so_z, const int64_t so_h, const int64_t so_n, float scale_log2,
+                     int causal) {
+  constexpr int DPL = MAXD / 32;  // output columns per lane
+  __shared__ float qs[4][MAXD];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row_id = (int64_t)blockIdx.x * 4 + warp;
+  const int64_t total = (int64_t)Z * H * N_CTX;
+  if (row_id >= total) return;
+  const int qi = (int)(row_id % N_CTX);
+  const int h = (int)((row_id / N_CTX) % H);
+  const int z = (int)(row_id / ((int64_t)N_CTX * H));
+  const T *qp = Q + z * sq_z + h * sq_h + (int64_t)qi * sq_n;
+  const T *kp = K + z * sk_z + h * sk_h;
+  const T *vp = V + z * sv_z + h * sv_h;
+  for (int d = lane; d < D; d += 32) qs[warp][d] = to_f32<T>(qp[d]);
+  __syncwarp();
+  float acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  const int kv_end = causal ? qi + 1 : N_CTX;
+  for (int kv0 = 0; kv0 < kv_end; kv0 += 32) {
+    const int kv = kv0 + lane;
+    float s = -INFINITY;
+    if (kv < kv_end) {
+      const T *kr = kp + (int64_t)kv * sk_n;
+      float dot = 0.f;
+      for (int d = 0; d < D; ++d) dot = fmaf(qs[warp][d], to_f32<T>(kr[d]), dot);
+      s = dot * scale_log2;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float pe = (kv < kv_end) ? exp2f(s - m_new) : 0.f;
+    const float alpha = exp2f(m - m_new);  // m == -inf on the first step: alpha = 0, acc and l are 0
+    l = l * alpha + warp_sum(pe);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] *= alpha;
+    const int nvalid = kv_end - kv0 < 32 ? kv_end - kv0 : 32;
+    for (int t = 0; t < nvalid; ++t) {
+      const float pt = __shfl_sync(0xffffffffu, pe, t);
+      const T *vr = vp + (int64_t)(kv0 + t) * sv_n;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        const int d = lane + i * 32;
+        if (d < D) acc[i] = fmaf(pt, to_f32<T>(vr[d]), acc[i]);
+      }
+    }
+  }
+  T *op = O + z * so_z + h * so_h + (int64_t)qi * so_n;
+  const float inv = 1.0f / l;
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) {
+    const int d = lane + i * 32;
+    if (d < D) op[d] = from_f32<T>(acc[i] * inv);
+  }
+}
+
+template <typename T>
+static int launch_simt(const T *Q, const T *K, const T *V, T *O, int64_t Z, int64_t H, int64_t N,
+                       int64_t D, const int64_t *s, float scale_log2, int causal, cudaStream_t st) {
+  if (D > 256) return HEXB_ERR_UNSUPPORTED;
+  const int64_t rows = Z * H * N;
+  const int64_t ctas = (rows + 3) / 4;
+  if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
+  if (D <= 64)
+    attn_fwd_simt_kernel<T, 64><<<(unsigned)ctas, 128, 0, st>>>(Q, K, V, O, (int)Z, (int)H, (int)N, (int)D,
+        s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7], s[8], s[9], s[10], s[11], scale_log2, causal);
+  else if (D <= 128)
+    attn_fwd_simt_kernel<T, 128><<<(unsigned)ctas, 128, 0, st>>>(Q, K, V, O, (int)Z, (int)H, (int)N, (int)D,
+        s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7], s[8], s[9], s[10], s[11], scale_log2, causal);
+  else
+    attn_fwd_simt_kernel<T, 256><<<(unsigned)ctas, 128, 0, st>>>(Q, K, V, O, (int)Z, (int)H, (int)N, (int)D,
+        s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7], s[8], s[9], s[10], s[11], scale_log2, causal);
+  return check_launch("attn_simt");
+}
+
+template <int HD>
+static int launch_tc(const __half *Q, const __half *K, const __half *V, __half *O, int64_t Z, int64_t H,
+                     int64_t N, const int64_t *s, float scale_log2, int causal, cudaStream_t st) {
+  using cfg = Cfg<HD>;
+  CUtensorMap tm[3];
+  const __half *base[3] = {Q, K, V};
+  for (int i = 0; i < 3; ++i) {
+    const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)N, (uint64_t)H, (uint64_t)Z};
+    const uint64_t strides[3] = {(uint64_t)s[3 * i + 2] * 2, (uint64_t)s[3 * i + 1] * 2,
+                                 (uint64_t)s[3 * i + 0] * 2};
+    const uint32_t box[4] = {64, 128, 1, 1};
+    if (int e = encode_tmap_f16_sw128(&tm[i], base[i], 4, dims, strides, box)) return e;
+  }
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = attn_fwd_tc_kernel<HD>;
+  if (!attr_done[dev & 63]) {
+    HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
+    attr_done[dev & 63] = true;
+  }
+  Params p;
+  p.out = O;
+  p.so_z = s[9]; p.so_h = s[10]; p.so_n = s[11];
+  p.Z = (int)Z; p.H = (int)H; p.N_CTX = (int)N;
+  p.num_q_tiles = (int)((N + BLOCK_M - 1) / BLOCK_M);
+  p.scale_log2 = scale_log2;
+  p.causal = causal ? 1 : 0;
+  p.out_vec_ok = aligned16(O) && s[9] % 8 == 0 && s[10] % 8 == 0 && s[11] % 8 == 0;
+  p.v_lbo = (uint32_t)option("attn_v_lbo", cfg::CHUNK_BYTES);
+  p.v_sbo = (uint32_t)option("attn_v_sbo", 1024);
+  const int64_t ctas = (int64_t)p.num_q_tiles * Z * H;
+  if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
+  kern<<<(unsigned)ctas, THREADS, cfg::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2], p);
+  return check_launch("attn_tc");
+}
+
+}  // namespace attn
+
+int attn_device_status_fetch_and_clear(int *out) {
+  int v = 0, zero = 0;
+  HEXB_CUDA_OK(cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int)));
+  if (v) HEXB_CUDA_OK(cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int)));
+  *out = v;
+  return HEXB_OK;
+}
+
+static int attn_check(const void *Q, const void *K, const void *V, void *O, int64_t Z, int64_t H,
+                      int64_t N, int64_t D, const int64_t *s, float scale) {
+  if (Z < 0 || H < 0 || N < 0 || D < 0) return HEXB_ERR_BAD_ARG;
+  if (Z == 0 || H == 0 || N == 0 || D == 0) return 1;  // nothing to do
+  if (!Q || !K || !V || !O || !s) return HEXB_ERR_BAD_ARG;
+  if (!(scale > 0.f)) return HEXB_ERR_BAD_ARG;
+  for (int i = 0; i < 12; ++i)
+    if (s[i] < 0) return HEXB_ERR_BAD_ARG;
+  for (int t = 0; t < 4; ++t)
+    if (s[3 * t + 2] < D) return HEXB_ERR_BAD_ARG;
+  if (N >= (1ll << 31) || H >= (1ll << 31) || Z >= (1ll << 31)) return HEXB_ERR_UNSUPPORTED;
+  return HEXB_OK;
+}
+
+}  // namespace hexb
+
+extern "C" int hexb_attention_fwd_f16(const void *Q, const void *K, const void *V, void *Out, int64_t Z,
+                                      int64_t H, int64_t N, int64_t D, const int64_t *s, float sm_scale,
+                                      int causal, void *stream) {
+  using namespace hexb;
+  const int c = attn_check(Q, K, V, Out, Z, H, N, D, s, sm_scale);
+  if (c == 1) return HEXB_OK;
+  if (c) return c;
+  DeviceInfo di;
+  if (int e = current_device(&di)) return e;
+  const float scale_log2 = sm_scale * 1.44269504f;
+  bool tma_ok = (D == 64 || D == 128) && !option("attn_force_simt", 0) && aligned16(Q) && aligned16(K) &&
+                aligned16(V);
+  for (int i = 0; i < 9 && tma_ok; ++i) tma_ok = s[i] % 8 == 0 && s[i] > 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tma_ok) {
+    if (D == 128)
+      return attn::launch_tc<128>((const __half *)Q, (const __half *)K, (const __half *)V, (__half *)Out,
+                                  Z, H, N, s, scale_log2, causal, st);
+    return attn::launch_tc<64>((const __half *)Q, (const __half *)K, (const __half *)V, (__half *)Out, Z,
+                               H, N, s, scale_log2, causal, st);
+  }
+  return attn::launch_simt<__half>((const __half *)Q, (const __half *)K, (const __half *)V, (__half *)Out,
+                                   Z, H, N, D, s, scale_log2, causal, st);
+}
+
+extern "C" int hexb_attention_fwd_f32(const float *Q, const float *K, const float *V, float *Out,
+                                      int64_t Z, int64_t H, int64_t N, int64_t D, const int64_t *s,
+                                      float sm_scale, int causal, void *stream) {
+  using namespace hexb;
+  const int c = attn_check(Q, K, V, Out, Z, H, N, D, s, sm_scale);
+  if (c == 1) return HEXB_OK;
+  if (c) return c;
+  DeviceInfo di;
+  if (int e = current_device(&di)) return e;
+  return attn::launch_simt<float>(Q, K, V, Out, Z, H, N, D, s, sm_scale * 1.44269504f, causal,
+                                  (cudaStream_t)stream);
+}

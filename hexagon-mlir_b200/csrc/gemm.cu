@@ -1,0 +1,370 @@
+// fp16 matmul with fp32 accumulation on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
+//
+// Reference semantics: matmul(A, B, C, N_ROWS, N_COLUMNS, N_INNER)
+// (test/python/triton/test_matmul.py:35-70) and the HexKL runtime call
+// hexkl_matmul_f16f16_f32 (qcom_hexagon_backend/bin/runtime/src/HexKLAPI.cpp:15-141) of
+// qualcomm/hexagon-mlir: C[M,N] = A[M,K] @ B[K,N], everything row-major.  The HexKL loop re-lays
+// out one 32x32 weight tile from DDR per (row tile, col tile, k tile) and accumulates in the fp16
+// HMX accumulator; this kernel accumulates in fp32 (TMEM) and rounds once.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: A tile [128 x 64] (K-major, 128-byte swizzle) and BN/64 B boxes
+//               [64 k x 64 n] (N-major, 128-byte swizzle) per k-block into a STAGES-deep smem ring;
+//   warp 1      MMA issuer: one thread issues 4 tcgen05.mma (128 x BN x 16) per k-block; the
+//               accumulator lives in TMEM and is double-buffered (2 x BN columns) so the epilogue of
+//               tile i overlaps the main loop of tile i+1;
+//   warps 2..5  epilogue: tcgen05.ld -> (+ residual) -> fp16/fp32 -> 16-byte global stores.
+// B is consumed as stored ([K, N] row-major = the "MN-major" operand form), no transpose pass.
+// Every mbarrier wait is bounded; on a timeout the CTA sets the status word and tears down.
+#include "tc_sm100.cuh"
+
+namespace hexb {
+
+static __device__ int g_gemm_status = 0;
+
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int THREADS = 192;
+
+template <int BN, int STAGES>
+struct Cfg {
+  static constexpr int B_BYTES = BK * BN * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+  static constexpr int TMEM_COLS = 2 * BN;
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(OutT *crow, const __half *rrow, const uint32_t (&acc)[32],
+                                                int col0, int N, bool vec_ok);
+
+template <>
+__device__ __forceinline__ void store_row_chunk<__half>(__half *crow, const __half *rrow,
+                                                        const uint32_t (&acc)[32], int col0, int N,
+                                                        bool vec_ok) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int c = col0 + g * 8;
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(acc[g * 8 + e]);
+    if (vec_ok && c + 8 <= N) {
+      if (rrow) {
+        Vec16<__half> r;
+        r.raw = *reinterpret_cast<const uint4 *>(rrow + c);
+        float rf[8];
+        r.unpack(rf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += rf[e];
+      }
+      Vec16<__half> o;
+      o.pack(f);
+      *reinterpret_cast<uint4 *>(crow + c) = o.raw;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (c + e < N) crow[c + e] = __float2half_rn(f[e] + (rrow ? __half2float(rrow[c + e]) : 0.f));
+    }
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_row_chunk<float>(float *crow, const __half *rrow,
+                                                       const uint32_t (&acc)[32], int col0, int N,
+                                                       bool vec_ok) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const int c = col0 + g * 4;
+    float f[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) f[e] = __uint_as_float(acc[g * 4 + e]);
+    if (rrow) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (c + e < N) f[e] += __half2float(rrow[c + e]);
+    }
+    if (vec_ok && c + 4 <= N) {
+      *reinterpret_cast<float4 *>(crow + c) = make_float4(f[0], f[1], f[2], f[3]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (c + e < N) crow[c + e] = f[e];
+    }
+  }
+}
+
+template <int BN, int STAGES, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
+               int64_t ldr, int tiles_m, int tiles_n, int vec_ok, uint32_t b_lbo, uint32_t b_sbo) {
+  using cfg = Cfg<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = tc::smem_u32(smem_raw);
+  const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+  uint8_t *smem = smem_raw + pad;
+  const uint32_t smem_addr = raw_addr + pad;
+
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * cfg::STAGE_BYTES);
+  const uint32_t bar0 = smem_addr + STAGES * cfg::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tc::mbar_init(full_bar(s), 1);
+      tc::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      tc::mbar_init(tfull_bar(a), 1);
+      tc::mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::prefetch_tensormap(&tmA);
+    tc::prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tc::smem_u32(tmem_slot), cfg::TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!tc::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t sa = smem_addr + stage * cfg::STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          tc::mbar_arrive_expect_tx(full_bar(stage), cfg::STAGE_BYTES);
+          tc::tma_load_2d(sa, &tmA, kb * BK, tm * BM, full_bar(stage));
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j)
+            tc::tma_load_2d(sb + j * (BK * 128), &tmB, tn * BN + j * 64, kb * BK, full_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::make_idesc_f16_f32(BM, BN, 0, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int t = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+        const int acc = t & 1;
+        if (!tc::mbar_wait(tempty_bar(acc), ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag)) break;
+        tc::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!tc::mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          tc::tc_fence_after();
+          const uint32_t sa = smem_addr + stage * cfg::STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const uint64_t adesc = tc::make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bdesc = tc::make_smem_desc_sw128(sb, b_lbo, b_sbo);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // A: +32 bytes inside the 128-byte swizzle row; B: +16 k-rows = 2 swizzle atoms.
+            tc::mma_f16_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), idesc,
+                           (kb | k) != 0 ? 1u : 0u);
+          }
+          tc::mma_commit(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc::mma_commit(tfull_bar(acc));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int t = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      const int acc = t & 1;
+      if (!tc::mbar_wait(tfull_bar(acc), (uint32_t)(t >> 1) & 1u, abort_flag)) break;
+      tc::tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+      OutT *crow = C + (int64_t)row * ldc;
+      const __half *rrow = R ? R + (int64_t)row * ldr : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
+        tc::tmem_ld_wait();
+        const int col0 = tn * BN + c * 32;
+        if (row < M && col0 < N) store_row_chunk<OutT>(crow, rrow, v, col0, N, vec_ok != 0);
+      }
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);  // let copies in flight land before the CTA retires
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, cfg::TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_status, (int)HEXB_ERR_TIMEOUT);
+}
+
+// Any shape / alignment / K == 0: plain CUDA-core tiles.  Only the shapes the tensor-core path
+// cannot take (leading dimensions or pointers that break the 16-byte TMA rule) land here.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(const __half *__restrict__ A, const __half *__restrict__ B, OutT *__restrict__ C,
+                 const __half *__restrict__ R, int64_t M, int64_t N, int64_t K, int64_t lda,
+                 int64_t ldb, int64_t ldc, int64_t ldr) {
+  __shared__ float As[16][17], Bs[16][17];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int64_t row = (int64_t)blockIdx.y * 16 + ty, col = (int64_t)blockIdx.x * 16 + tx;
+  float acc = 0.f;
+  for (int64_t k0 = 0; k0 < K; k0 += 16) {
+    As[ty][tx] = (row < M && k0 + tx < K) ? __half2float(A[row * lda + k0 + tx]) : 0.f;
+    Bs[ty][tx] = (k0 + ty < K && col < N) ? __half2float(B[(k0 + ty) * ldb + col]) : 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) acc = fmaf(As[ty][k], Bs[k][tx], acc);
+    __syncthreads();
+  }
+  if (row < M && col < N) {
+    if (R) acc += __half2float(R[row * ldr + col]);
+    C[row * ldc + col] = from_f32<OutT>(acc);
+  }
+}
+
+template <int BN, int STAGES, typename OutT>
+static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M,
+                     int N, int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count,
+                     cudaStream_t st) {
+  using cfg = Cfg<BN, STAGES>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = gemm_tc_kernel<BN, STAGES, OutT>;
+  if (!attr_done[dev & 63]) {
+    HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
+    attr_done[dev & 63] = true;
+  }
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int tiles = tiles_m * tiles_n;
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  const uint32_t lbo = (uint32_t)option("gemm_b_lbo", BK * 128);
+  const uint32_t sbo = (uint32_t)option("gemm_b_sbo", 1024);
+  kern<<<grid, THREADS, cfg::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n,
+                                               vec_ok, lbo, sbo);
+  return check_launch("gemm_tc");
+}
+
+template <typename OutT>
+static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *R, int64_t M, int64_t N,
+                       int64_t K, int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t st) {
+  DeviceInfo di;
+  if (int s = current_device(&di)) return s;
+  const int64_t ldr = ldc;
+  const bool tc_ok = K > 0 && lda % 8 == 0 && ldb % 8 == 0 && aligned16(A) && aligned16(B) &&
+                     M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31) &&
+                     !option("gemm_force_simt", 0);
+  if (!tc_ok) {
+    dim3 grid((unsigned)((N + 15) / 16), (unsigned)((M + 15) / 16));
+    if (grid.y > 65535) return HEXB_ERR_UNSUPPORTED;
+    gemm_simt_kernel<OutT><<<grid, 256, 0, st>>>(A, B, C, R, M, N, K, lda, ldb, ldc, ldr);
+    return check_launch("gemm_simt");
+  }
+  CUtensorMap tmA, tmB;
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t strides[1] = {(uint64_t)lda * 2};
+    const uint32_t box[2] = {BK, BM};
+    if (int s = encode_tmap_f16_sw128(&tmA, A, 2, dims, strides, box)) return s;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+    const uint64_t strides[1] = {(uint64_t)ldb * 2};
+    const uint32_t box[2] = {64, BK};
+    if (int s = encode_tmap_f16_sw128(&tmB, B, 2, dims, strides, box)) return s;
+  }
+  constexpr int EV = 16 / (int)sizeof(OutT);
+  const int vec_ok = (ldc % EV == 0) && aligned16(C) && (!R || (sizeof(OutT) == 2 && aligned16(R)));
+  const int tiles_m = (int)((M + BM - 1) / BM);
+  int bn = option("gemm_bn", 0);
+  if (bn != 64 && bn != 128 && bn != 256) {
+    bn = 256;
+    if (N <= 64 || (int64_t)tiles_m * ((N + 127) / 128) < di.sm_count / 2) bn = 64;
+    else if (N <= 128 || (int64_t)tiles_m * ((N + 255) / 256) < di.sm_count) bn = 128;
+  }
+  switch (bn) {
+    case 64:
+      return launch_tc<64, 8, OutT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+    case 128:
+      return launch_tc<128, 6, OutT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+    default:
+      return launch_tc<256, 4, OutT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+  }
+}
+
+}  // namespace gemm
+
+int gemm_device_status_fetch_and_clear(int *out) {
+  int v = 0, zero = 0;
+  HEXB_CUDA_OK(cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)));
+  if (v) HEXB_CUDA_OK(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int)));
+  *out = v;
+  return HEXB_OK;
+}
+
+}  // namespace hexb
+
+extern "C" int hexb_matmul_f16(const void *A, const void *B, void *C, const void *residual, int64_t M,
+                               int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                               int out_dtype, void *stream) {
+  using namespace hexb;
+  if (M < 0 || N < 0 || K < 0) return HEXB_ERR_BAD_ARG;
+  if (out_dtype != HEXB_DT_F16 && out_dtype != HEXB_DT_F32) return HEXB_ERR_UNSUPPORTED;
+  if (M == 0 || N == 0) return HEXB_OK;
+  if (!C || (K > 0 && (!A || !B))) return HEXB_ERR_BAD_ARG;
+  if (lda < K || ldb < N || ldc < N) return HEXB_ERR_BAD_ARG;
+  if (out_dtype == HEXB_DT_F16)
+    return gemm::matmul_impl<__half>((const __half *)A, (const __half *)B, (__half *)C,
+                                     (const __half *)residual, M, N, K, lda, ldb, ldc, (cudaStream_t)stream);
+  return gemm::matmul_impl<float>((const __half *)A, (const __half *)B, (float *)C,
+                                  (const __half *)residual, M, N, K, lda, ldb, ldc, (cudaStream_t)stream);
+}
+
+extern "C" int hexkl_matmul_f16f16_f32(int64_t n_row, int64_t n_col, int64_t n_inner, float *outM,
+                                       const void *inAct, const void *inW) {
+  return hexb_matmul_f16(inAct, inW, outM, nullptr, n_row, n_col, n_inner, n_inner, n_col, n_col,
+                         HEXB_DT_F32, nullptr);
+}

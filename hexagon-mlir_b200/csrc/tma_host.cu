@@ -1,0 +1,74 @@
+// Host side of the TMA path: tensor-map encoding through the driver entry point, and the
+// aggregated device status word.
+#include <mutex>
+
+#include "tc_sm100.cuh"
+
+namespace hexb {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+int encode_tmap_f16_sw128(CUtensorMap *out, const void *base, int rank, const uint64_t *dims,
+                          const uint64_t *strides_bytes, const uint32_t *box) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_cuda_error(cudaErrorNotSupported, "cuTensorMapEncodeTiled entry point");
+    return HEXB_ERR_CUDA;
+  }
+  if (rank < 2 || rank > 5) return HEXB_ERR_BAD_ARG;
+  if (!aligned16(base)) return HEXB_ERR_MISALIGNED;
+  cuuint64_t gd[5], gs[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    gd[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (dims[i] == 0) return HEXB_ERR_BAD_ARG;
+  }
+  for (int i = 0; i + 1 < rank; ++i) {
+    gs[i] = strides_bytes[i];
+    if (gs[i] % 16) return HEXB_ERR_MISALIGNED;
+  }
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void *>(base), gd,
+                  gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+    return HEXB_ERR_CUDA;
+  }
+  return HEXB_OK;
+}
+
+int gemm_device_status_fetch_and_clear(int *out);
+int attn_device_status_fetch_and_clear(int *out);
+
+}  // namespace hexb
+
+extern "C" int hexb_device_status(int *out) {
+  using namespace hexb;
+  if (!out) return HEXB_ERR_BAD_ARG;
+  HEXB_CUDA_OK(cudaDeviceSynchronize());
+  int a = 0, b = 0;
+  if (int s = gemm_device_status_fetch_and_clear(&a)) return s;
+  if (int s = attn_device_status_fetch_and_clear(&b)) return s;
+  *out = a ? a : b;
+  return HEXB_OK;
+}

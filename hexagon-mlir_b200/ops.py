@@ -1,0 +1,268 @@
+"""Tensor-level entry points over the C ABI.
+
+Every function writes into caller-provided output tensors (the reference launcher copies results
+back into the tensors the test passed, qcom_hexagon_backend/backend/triton_hexagon_launcher.py:716-728)
+and returns nothing useful.  CUDA tensors are used in place on the current stream; CPU tensors go
+through the `_host` entry points, which stage them across PCIe inside the call.  PyTorch is used
+for memory and streams only; all arithmetic happens in libhexb200.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib
+from ._lib import HEXB_DT_F16, HEXB_DT_F32, check
+
+_DT = {torch.float16: HEXB_DT_F16, torch.float32: HEXB_DT_F32}
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype not in _DT:
+        raise TypeError(f"unsupported dtype {t.dtype}: the kernels take float16 and float32")
+    return _DT[t.dtype]
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _same_place(*ts):
+    ts = [t for t in ts if t is not None]
+    dev = ts[0].device
+    for t in ts:
+        if t.device != dev:
+            raise ValueError("all tensors of one call must live on the same device")
+    return dev
+
+
+def _rows2d(t: torch.Tensor, what: str):
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise ValueError(f"{what}: expected a 2-D tensor with unit inner stride")
+    return t.shape[0], t.shape[1], (t.stride(0) if t.shape[0] > 1 else max(t.shape[1], t.stride(0)))
+
+
+def softmax(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, :] = softmax(x[r, :]) (reference: test/python/triton/test_softmax.py:44-72)."""
+    lib = _lib.load()
+    dev = _same_place(x, out)
+    rows, cols, xs = _rows2d(x, "x")
+    r2, c2, ys = _rows2d(out, "out")
+    if (rows, cols) != (r2, c2) or x.dtype != out.dtype:
+        raise ValueError("softmax: x and out differ in shape or dtype")
+    if dev.type == "cuda":
+        with torch.cuda.device(dev):
+            fn = lib.hexb_softmax_f16 if x.dtype == torch.float16 else lib.hexb_softmax_f32
+            _dt(x)
+            check(fn(_ptr(x), _ptr(out), rows, cols, xs, ys, _stream(x)), "softmax")
+    else:
+        if not (x.is_contiguous() and out.is_contiguous()):
+            raise ValueError("softmax: host tensors must be contiguous")
+        check(lib.hexb_softmax_host(_dt(x), _ptr(x), _ptr(out), rows, cols), "softmax_host")
+
+
+def layer_norm(x, out, weight, bias, mean=None, rstd=None, eps: float = 1e-5) -> None:
+    """LayerNorm forward (reference: test/python/triton/test_layer_norm.py:42-82).
+
+    mean / rstd, when given, receive the per-row statistics.  They may be float32 or x's dtype (the
+    reference allocates them in x's dtype); the kernel produces float32.
+    """
+    lib = _lib.load()
+    dev = _same_place(x, out, weight, bias, mean, rstd)
+    rows, cols, xs = _rows2d(x, "x")
+    r2, c2, ys = _rows2d(out, "out")
+    if (rows, cols) != (r2, c2) or not (x.dtype == out.dtype == weight.dtype == bias.dtype):
+        raise ValueError("layer_norm: shape or dtype mismatch")
+    if weight.numel() != cols or bias.numel() != cols:
+        raise ValueError("layer_norm: weight/bias must have NUM_COLS elements")
+    stats = []
+    for s in (mean, rstd):
+        if s is None:
+            stats.append((None, None))
+        elif s.dtype == torch.float32 and s.is_contiguous():
+            stats.append((s, None))
+        else:
+            stats.append((torch.empty(rows, dtype=torch.float32, device=dev), s))
+    m32, r32 = stats[0][0], stats[1][0]
+    if dev.type == "cuda":
+        with torch.cuda.device(dev):
+            fn = lib.hexb_layer_norm_f16 if x.dtype == torch.float16 else lib.hexb_layer_norm_f32
+            _dt(x)
+            check(fn(_ptr(x), _ptr(out), _ptr(weight.contiguous()), _ptr(bias.contiguous()), _ptr(m32),
+                     _ptr(r32), rows, cols, xs, ys, float(eps), _stream(x)), "layer_norm")
+    else:
+        if not (x.is_contiguous() and out.is_contiguous()):
+            raise ValueError("layer_norm: host tensors must be contiguous")
+        check(lib.hexb_layer_norm_host(_dt(x), _ptr(x), _ptr(out), _ptr(weight.contiguous()),
+                                       _ptr(bias.contiguous()), _ptr(m32), _ptr(r32), rows, cols,
+                                       float(eps)), "layer_norm_host")
+    for tmp, dst in stats:
+        if dst is not None:
+            dst.copy_(tmp.to(dst.dtype).reshape(dst.shape))
+
+
+def rms_norm(x, out, weight, eps: float = 1e-6) -> None:
+    """RMSNorm forward (reference: test/python/triton/test_rms_norm.py:37-63)."""
+    lib = _lib.load()
+    dev = _same_place(x, out, weight)
+    rows, cols, xs = _rows2d(x, "x")
+    r2, c2, ys = _rows2d(out, "out")
+    if (rows, cols) != (r2, c2) or not (x.dtype == out.dtype == weight.dtype):
+        raise ValueError("rms_norm: shape or dtype mismatch")
+    if weight.numel() != cols:
+        raise ValueError("rms_norm: weight must have NUM_COLS elements")
+    if dev.type == "cuda":
+        with torch.cuda.device(dev):
+            fn = lib.hexb_rms_norm_f16 if x.dtype == torch.float16 else lib.hexb_rms_norm_f32
+            _dt(x)
+            check(fn(_ptr(x), _ptr(out), _ptr(weight.contiguous()), rows, cols, xs, ys, float(eps),
+                     _stream(x)), "rms_norm")
+    else:
+        if not (x.is_contiguous() and out.is_contiguous()):
+            raise ValueError("rms_norm: host tensors must be contiguous")
+        check(lib.hexb_rms_norm_host(_dt(x), _ptr(x), _ptr(out), _ptr(weight.contiguous()), rows, cols,
+                                     float(eps)), "rms_norm_host")
+
+
+def matmul(a, b, c, residual=None) -> None:
+    """c = a @ b (+ residual); a, b float16 row-major, c float16 or float32, fp32 accumulation.
+
+    Reference: test/python/triton/test_matmul.py:35-70, docs/tutorials/triton/matmul_hexkl.md:61-97.
+    """
+    lib = _lib.load()
+    dev = _same_place(a, b, c, residual)
+    if a.dtype != torch.float16 or b.dtype != torch.float16:
+        raise TypeError("matmul: A and B must be float16")
+    M, K, lda = _rows2d(a, "A")
+    K2, N, ldb = _rows2d(b, "B")
+    M2, N2, ldc = _rows2d(c, "C")
+    if K != K2 or M != M2 or N != N2:
+        raise ValueError("matmul: shapes do not agree")
+    if dev.type == "cuda":
+        if residual is not None:
+            if residual.dtype != torch.float16 or residual.shape != c.shape or residual.stride(0) != c.stride(0):
+                raise ValueError("matmul: residual must be float16 with C's shape and leading dimension")
+        with torch.cuda.device(dev):
+            check(lib.hexb_matmul_f16(_ptr(a), _ptr(b), _ptr(c), _ptr(residual), M, N, K, lda, ldb, ldc,
+                                      _dt(c), _stream(a)), "matmul")
+    else:
+        if residual is not None:
+            raise ValueError("matmul: residual is a device-path feature")
+        if not (a.is_contiguous() and b.is_contiguous() and c.is_contiguous()):
+            raise ValueError("matmul: host tensors must be contiguous")
+        check(lib.hexb_matmul_f16_host(_ptr(a), _ptr(b), _ptr(c), M, N, K, _dt(c)), "matmul_host")
+
+
+def hexkl_matmul_f16f16_f32(n_row, n_col, n_inner, out, act, w) -> None:
+    """The HexKL runtime symbol, same argument order (bin/runtime/include/HexKLAPI.h:16-21); device tensors."""
+    lib = _lib.load()
+    with torch.cuda.device(out.device):
+        torch.cuda.current_stream().synchronize()  # the symbol runs on the legacy default stream
+        check(lib.hexkl_matmul_f16f16_f32(n_row, n_col, n_inner, _ptr(out), _ptr(act), _ptr(w)), "hexkl_matmul")
+        torch.cuda.synchronize()
+
+
+def attention(q, k, v, out, sm_scale=None, causal: bool = False) -> None:
+    """out = softmax(q k^T * sm_scale [+ causal mask]) v for [Z, H, N_CTX, D] tensors.
+
+    Reference: test/python/triton/test_flash_attention.py:37-168.  Any strides with a unit
+    innermost stride are accepted on the device path.
+    """
+    lib = _lib.load()
+    dev = _same_place(q, k, v, out)
+    if not (q.dim() == k.dim() == v.dim() == out.dim() == 4):
+        raise ValueError("attention: expected [Z, H, N_CTX, D] tensors")
+    if not (q.shape == k.shape == v.shape == out.shape) or not (q.dtype == k.dtype == v.dtype == out.dtype):
+        raise ValueError("attention: q, k, v, out must agree in shape and dtype")
+    Z, H, N, D = q.shape
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    dt = _dt(q)
+    if dev.type == "cuda":
+        strides = []
+        for t in (q, k, v, out):
+            if D > 1 and t.stride(3) != 1:
+                raise ValueError("attention: innermost stride must be 1")
+            strides += [t.stride(0), t.stride(1), t.stride(2)]
+        arr = (C.c_int64 * 12)(*strides)
+        with torch.cuda.device(dev):
+            fn = lib.hexb_attention_fwd_f16 if dt == HEXB_DT_F16 else lib.hexb_attention_fwd_f32
+            check(fn(_ptr(q), _ptr(k), _ptr(v), _ptr(out), Z, H, N, D, arr, float(sm_scale), int(bool(causal)),
+                     _stream(q)), "attention")
+    else:
+        if not all(t.is_contiguous() for t in (q, k, v, out)):
+            raise ValueError("attention: host tensors must be contiguous")
+        check(lib.hexb_attention_fwd_host(dt, _ptr(q), _ptr(k), _ptr(v), _ptr(out), Z, H, N, D,
+                                          float(sm_scale), int(bool(causal))), "attention_host")
+
+
+def silu(x, out) -> None:
+    """out = x / (1 + exp(-x)) (reference: test/python/triton/test_silu.py:38-52)."""
+    lib = _lib.load()
+    dev = _same_place(x, out)
+    if x.shape != out.shape or x.dtype != out.dtype or not (x.is_contiguous() and out.is_contiguous()):
+        raise ValueError("silu: x and out must be contiguous with equal shape and dtype")
+    host = dev.type != "cuda"
+    xd, od = (x.cuda(), torch.empty_like(x, device="cuda")) if host else (x, out)
+    with torch.cuda.device(xd.device):
+        fn = lib.hexb_silu_f16 if _dt(x) == HEXB_DT_F16 else lib.hexb_silu_f32
+        check(fn(_ptr(xd), _ptr(od), x.numel(), _stream(xd)), "silu")
+    if host:
+        out.copy_(od)
+
+
+def swiglu(gate_up, out) -> None:
+    """out[r, c] = silu(gate_up[r, c]) * gate_up[r, cols + c]; float16 device tensors."""
+    lib = _lib.load()
+    _same_place(gate_up, out)
+    rows, cols2 = gate_up.shape
+    if gate_up.dtype != torch.float16 or out.dtype != torch.float16 or out.shape != (rows, cols2 // 2):
+        raise ValueError("swiglu: expected float16 [rows, 2*cols] -> [rows, cols]")
+    if not (gate_up.is_contiguous() and out.is_contiguous()):
+        raise ValueError("swiglu: tensors must be contiguous")
+    with torch.cuda.device(gate_up.device):
+        check(lib.hexb_swiglu_f16(_ptr(gate_up), _ptr(out), rows, cols2 // 2, _stream(gate_up)), "swiglu")
+
+
+class DecoderStack:
+    """The decoder-only block stack on one GPU: holds the weight pointer tables and the workspace.
+
+    weights: list (one dict per layer) with float16 CUDA tensors wqkv [d, 3d], wo [d, d],
+    wgu [d, 2*d_ff], wd [d_ff, d], g1 [d], g2 [d].
+    """
+
+    def __init__(self, weights, n_heads: int, head_dim: int, d_ff: int, batch: int, seq: int,
+                 rms_eps: float = 1e-6):
+        self.lib = _lib.load()
+        self.weights = weights
+        d_model = n_heads * head_dim
+        self.cfg = _lib.DecoderConfig(len(weights), d_model, n_heads, head_dim, d_ff, batch, seq, rms_eps)
+        self.device = weights[0]["wqkv"].device if weights else torch.device("cuda")
+        n = len(weights)
+        self._tables = {}
+        for name in ("wqkv", "wo", "wgu", "wd", "g1", "g2"):
+            for w in weights:
+                t = w[name]
+                if t.dtype != torch.float16 or not t.is_contiguous() or t.device != self.device:
+                    raise ValueError(f"decoder weight {name}: float16 contiguous CUDA tensor expected")
+            self._tables[name] = (C.c_void_p * max(n, 1))(*[w[name].data_ptr() for w in weights])
+        self.cweights = _lib.DecoderWeights(*[C.cast(self._tables[k], C.POINTER(C.c_void_p))
+                                              for k in ("wqkv", "wo", "wgu", "wd", "g1", "g2")])
+        self.ws_bytes = self.lib.hexb_decoder_workspace_bytes(C.byref(self.cfg))
+        self.workspace = torch.empty(max(self.ws_bytes, 256), dtype=torch.uint8, device=self.device)
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        """x, out: float16 CUDA [batch*seq, d_model] (or [batch, seq, d_model]) contiguous."""
+        if x.dtype != torch.float16 or out.dtype != torch.float16 or not (x.is_contiguous() and out.is_contiguous()):
+            raise ValueError("decoder: float16 contiguous tensors expected")
+        if x.numel() != self.cfg.batch * self.cfg.seq * self.cfg.d_model or out.numel() != x.numel():
+            raise ValueError("decoder: x/out size does not match the configuration")
+        with torch.cuda.device(self.device):
+            check(self.lib.hexb_decoder_forward_f16(C.byref(self.cfg), C.byref(self.cweights), _ptr(x), _ptr(out),
+                                                    _ptr(self.workspace), self.ws_bytes, _stream(x)), "decoder_forward")

@@ -1,0 +1,169 @@
+/*
+ * hexb.h -- C ABI of libhexb200: the hexagon-mlir kernel set (row softmax, LayerNorm, RMSNorm,
+ * fp16 matmul, flash-attention forward, decoder block stack) as hand-written sm_100a CUDA kernels.
+ *
+ * Conventions (all entry points):
+ *   - plain pointers and sizes, no C++ or torch types; every function returns an int status
+ *     (HEXB_OK == 0, negative on error) and never aborts, traps or throws;
+ *   - unless the name ends in `_host`, pointer arguments are DEVICE pointers on the current CUDA
+ *     device; the call is asynchronous and ordered on `stream` (a cudaStream_t passed as void*,
+ *     NULL = the legacy default stream);
+ *   - strides are in ELEMENTS, with the meaning of the reference's memref strides
+ *     (qcom_hexagon_backend: test/utils/dsp/include/common.h:15-27);
+ *   - the caller owns every tensor; outputs are written in place, nothing is returned;
+ *   - `_host` entry points take HOST pointers, stage the tensors through device memory that the
+ *     library caches per device, and return after the result is back in host memory.
+ *
+ * Each declaration cites the reference interface it replaces (path inside qualcomm/hexagon-mlir).
+ */
+#ifndef HEXB_H_
+#define HEXB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes.  Replaces: AEE_SUCCESS / AEE_ENOMEMORY / AEE_EFAILED returned by
+ * hexkl_matmul_f16f16_f32 (qcom_hexagon_backend/bin/runtime/src/HexKLAPI.cpp:56-68) and the
+ * abort-on-CHECK convention of the device runtime (bin/runtime/include/HexagonCommon.h:28-64). */
+enum {
+  HEXB_OK = 0,
+  HEXB_ERR_BAD_ARG = -1,     /* null pointer, negative size, inconsistent strides            */
+  HEXB_ERR_UNSUPPORTED = -2, /* shape or dtype outside what the kernels implement            */
+  HEXB_ERR_MISALIGNED = -3,  /* pointer or stride not aligned as the entry point requires    */
+  HEXB_ERR_CUDA = -4,        /* a CUDA runtime / driver call failed (see hexb_last_cuda_error) */
+  HEXB_ERR_TIMEOUT = -5,     /* a device-side bounded wait gave up (see hexb_device_status)  */
+  HEXB_ERR_WORKSPACE = -6,   /* workspace missing or too small                               */
+  HEXB_ERR_NO_DEVICE = -7    /* no sm_100 device is current                                  */
+};
+
+/* dtype ids: the ids of the reference's raw tensor files (test/utils/dsp/include/tensor.h:26-38) */
+enum { HEXB_DT_F16 = 1, HEXB_DT_F32 = 2 };
+
+int hexb_version(void);
+const char *hexb_status_string(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char *hexb_last_cuda_error(void);
+/* Synchronises the current device, then reports and clears the sticky device-side status word
+ * that bounded waits inside the tensor-core kernels set when they give up.  *out = HEXB_OK or
+ * HEXB_ERR_TIMEOUT.  Replaces: DMAStatus out-param of the UserDMA runtime
+ * (bin/runtime/UserDMA/RuntimeDMA.h:18). */
+int hexb_device_status(int *out);
+
+/* ---- row softmax.  Replaces: softmax_kernel(x_ptr, output_ptr, NUM_ROWS, NUM_COLS, BLOCK_SIZE)
+ * (test/python/triton/test_softmax.py:44-72) and online_softmax(...)
+ * (test/python/triton/test_online_softmax.py:30-81).  y[r, :] = softmax(x[r, :]); fp32 math. */
+int hexb_softmax_f32(const float *x, float *y, int64_t rows, int64_t cols, int64_t x_row_stride,
+                     int64_t y_row_stride, void *stream);
+int hexb_softmax_f16(const void *x, void *y, int64_t rows, int64_t cols, int64_t x_row_stride,
+                     int64_t y_row_stride, void *stream);
+
+/* ---- LayerNorm forward.  Replaces: layer_norm_fwd_kernel(x_ptr, y_ptr, weights_ptr, biases_ptr,
+ * mean_ptr, rstd_ptr, BLOCK_SIZE, EPSILON, NUM_COLS, NUM_ROWS)
+ * (test/python/triton/test_layer_norm.py:42-82).  Biased variance in the centred two-pass form,
+ * fp32 statistics; mean/rstd (fp32, one per row) may be NULL. */
+int hexb_layer_norm_f32(const float *x, float *y, const float *weight, const float *bias,
+                        float *mean, float *rstd, int64_t rows, int64_t cols, int64_t x_row_stride,
+                        int64_t y_row_stride, float eps, void *stream);
+int hexb_layer_norm_f16(const void *x, void *y, const void *weight, const void *bias, float *mean,
+                        float *rstd, int64_t rows, int64_t cols, int64_t x_row_stride,
+                        int64_t y_row_stride, float eps, void *stream);
+
+/* ---- RMSNorm forward.  Replaces: rms_norm_fwd_kernel(x_ptr, y_ptr, weights_ptr, BLOCK_SIZE,
+ * EPSILON, NUM_COLS, NUM_ROWS) (test/python/triton/test_rms_norm.py:37-63). */
+int hexb_rms_norm_f32(const float *x, float *y, const float *weight, int64_t rows, int64_t cols,
+                      int64_t x_row_stride, int64_t y_row_stride, float eps, void *stream);
+int hexb_rms_norm_f16(const void *x, void *y, const void *weight, int64_t rows, int64_t cols,
+                      int64_t x_row_stride, int64_t y_row_stride, float eps, void *stream);
+
+/* ---- fp16 matmul, fp32 accumulation.  C[M,N] = A[M,K] @ B[K,N] (+ residual), all row-major with
+ * leading dimensions lda/ldb/ldc in elements.  out_dtype = HEXB_DT_F16 or HEXB_DT_F32.
+ * `residual` (fp16, same shape and leading dimension as C when out is fp16) may be NULL.
+ * Replaces: matmul(A, B, C, N_ROWS, N_COLUMNS, N_INNER) (test/python/triton/test_matmul.py:35-70)
+ * and matmul_hexkl (docs/tutorials/triton/matmul_hexkl.md:61-97). */
+int hexb_matmul_f16(const void *A, const void *B, void *C, const void *residual, int64_t M,
+                    int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int out_dtype,
+                    void *stream);
+
+/* Symbol-level drop-in for the HexKL runtime call: same name, argument order (rows, cols, inner,
+ * out first) and fp32 output; device pointers, legacy default stream.
+ * Replaces: hexkl_matmul_f16f16_f32 (qcom_hexagon_backend/bin/runtime/include/HexKLAPI.h:16-21). */
+int hexkl_matmul_f16f16_f32(int64_t n_row, int64_t n_col, int64_t n_inner, float *outM,
+                            const void *inAct, const void *inW);
+
+/* ---- flash-attention forward, fp16 in/out, fp32 online softmax in base 2.
+ * Tensors are [Z, H, N_CTX, D] addressed as base + z*stride_z + h*stride_h + n*stride_n + d
+ * (innermost stride 1), one stride triple per tensor: strides[0..2] = Q, [3..5] = K, [6..8] = V,
+ * [9..11] = Out.  causal != 0 masks keys above the diagonal (the additive -inf mask of
+ * tm_tensor.attention).  Replaces: attention_fwd_kernel(pid1, Q, K, V, sm_scale, Out, H, N_CTX,
+ * BLOCK_M, BLOCK_DMODEL, BLOCK_N, STAGE, stride_0..3) with _attn_fwd_inner
+ * (test/python/triton/test_flash_attention.py:37-168), the fp16 form
+ * test/python/mlir/hexkl_attention/input.mlir:5-168, and tm_tensor.attention
+ * (qcom_hexagon_backend/lib/Transforms/LowerTmTensor.cpp:70-235). */
+int hexb_attention_fwd_f16(const void *Q, const void *K, const void *V, void *Out, int64_t Z,
+                           int64_t H, int64_t N_CTX, int64_t D, const int64_t *strides,
+                           float sm_scale, int causal, void *stream);
+/* fp32 tensors (the dtype of the reference's own Triton test); same argument meaning. */
+int hexb_attention_fwd_f32(const float *Q, const float *K, const float *V, float *Out, int64_t Z,
+                           int64_t H, int64_t N_CTX, int64_t D, const int64_t *strides,
+                           float sm_scale, int causal, void *stream);
+
+/* ---- SiLU and SwiGLU gating.  Replaces: silu_kernel(x_ptr, output_ptr, BLOCK_SIZE)
+ * (test/python/triton/test_silu.py:38-52).  hexb_swiglu_f16: out[r, c] = silu(gu[r, c]) *
+ * gu[r, c + cols] for a [rows, 2*cols] gate|up matrix. */
+int hexb_silu_f32(const float *x, float *y, int64_t n, void *stream);
+int hexb_silu_f16(const void *x, void *y, int64_t n, void *stream);
+int hexb_swiglu_f16(const void *gate_up, void *out, int64_t rows, int64_t cols, void *stream);
+
+/* ---- decoder-only block stack, forward.  Pre-norm blocks:
+ *   h = x + Wo . Attn(RMSNorm(x) . Wqkv);  x' = h + Wd . (SiLU(Wg . n) * (Wu . n)), n = RMSNorm(h)
+ * causal attention, no bias, fp16 storage, fp32 accumulation and statistics.
+ * Per layer l the weights are row-major fp16: wqkv[l] [d_model, 3*d_model] (columns q|k|v, head-major),
+ * wo[l] [d_model, d_model], wgu[l] [d_model, 2*d_ff] (columns gate|up), wd[l] [d_ff, d_model],
+ * g1[l], g2[l] [d_model] RMSNorm gains.  x and out are [batch*seq, d_model] fp16.
+ * No single reference function: composed from rms_norm_fwd_kernel, matmul, attention_fwd_kernel and
+ * silu_kernel above, the way test/python/torch-mlir/gpt2lmheadmodel.py:143-169 runs a whole model. */
+typedef struct hexb_decoder_config {
+  int32_t n_layers, d_model, n_heads, head_dim, d_ff, batch, seq;
+  float rms_eps;
+} hexb_decoder_config;
+
+typedef struct hexb_decoder_weights { /* arrays of n_layers device pointers (host arrays) */
+  const void *const *wqkv, *const *wo, *const *wgu, *const *wd, *const *g1, *const *g2;
+} hexb_decoder_weights;
+
+size_t hexb_decoder_workspace_bytes(const hexb_decoder_config *cfg);
+int hexb_decoder_forward_f16(const hexb_decoder_config *cfg, const hexb_decoder_weights *w,
+                             const void *x, void *out, void *workspace, size_t workspace_bytes,
+                             void *stream);
+
+/* ---- host-buffer entry points (the launcher path).  Replace the generated wrapper main() that
+ * loads `<kernel>_t{i}.raw`, runs the kernel and dumps `<kernel>_o{i}.raw`
+ * (qcom_hexagon_backend/backend/triton_hexagon_launcher.py:111-123,
+ *  backend/hexagon_launcher_base.py:430-437): tensors cross the host/device boundary inside. */
+int hexb_softmax_host(int dtype, const void *x, void *y, int64_t rows, int64_t cols);
+int hexb_layer_norm_host(int dtype, const void *x, void *y, const void *weight, const void *bias,
+                         float *mean, float *rstd, int64_t rows, int64_t cols, float eps);
+int hexb_rms_norm_host(int dtype, const void *x, void *y, const void *weight, int64_t rows,
+                       int64_t cols, float eps);
+int hexb_matmul_f16_host(const void *A, const void *B, void *C, int64_t M, int64_t N, int64_t K,
+                         int out_dtype);
+int hexb_attention_fwd_host(int dtype, const void *Q, const void *K, const void *V, void *Out,
+                            int64_t Z, int64_t H, int64_t N_CTX, int64_t D, float sm_scale,
+                            int causal);
+/* Releases the cached staging memory of the current device. */
+int hexb_host_staging_release(void);
+
+/* ---- tuning knob for experiments: selects a kernel variant by name ("ln_variant", ...).
+ * Unknown keys return HEXB_ERR_BAD_ARG.  Replaces: the per-launch HexagonOptions overrides
+ * (qcom_hexagon_backend/backend/hexagon_options.py:16-107). */
+int hexb_set_option(const char *key, int value);
+int hexb_get_option(const char *key, int *value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HEXB_H_ */

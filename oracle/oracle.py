@@ -1,0 +1,239 @@
+"""TEST INFRASTRUCTURE, not product code: the CPU oracle of the kernel set.
+
+Two layers, both CPU-only:
+  * ``c_*``   -- ctypes calls into liboracle.so, the plain-C restatement in oracle.c of the
+                 reference's operator definitions (each C function cites the reference lines);
+  * ``torch_*`` -- the exact PyTorch CPU eager calls the reference's tests compare against
+                 (test/python/triton/test_softmax.py:93, test_layer_norm.py:111-113,
+                 test_rms_norm.py:85-87, test_matmul.py:90, test_flash_attention.py:212), computed in
+                 fp32 from the fp16 inputs where the data is fp16, so that a tolerance measures the
+                 kernel and not the comparator.
+plus the seeded input generators for the five benchmark configurations.  Only tests/, the smoke
+check and the cpu_baseline / reference arm of bench.py import this module.
+
+Parity status: pinned against torch CPU and against outputs of the reference's own Triton kernels
+executed in Triton's interpreter (tests/golden/*.npz, made by tests/golden/make_golden.py).  Parity
+with the Hexagon NPU's own approximations is unpinned (no Hexagon toolchain or device output).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = Path(__file__).resolve().parent
+_LIB = None
+
+
+def build() -> Path:
+    """Compiles oracle.c into liboracle.so with the committed Makefile."""
+    subprocess.run(["make", "-C", str(HERE), "liboracle.so"], check=True, capture_output=True)
+    return HERE / "liboracle.so"
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        path = HERE / "liboracle.so"
+        if not path.exists():
+            build()
+        _LIB = C.CDLL(str(path))
+    return _LIB
+
+
+def _p(t: torch.Tensor):
+    assert t.device.type == "cpu" and t.is_contiguous()
+    return C.c_void_p(t.data_ptr())
+
+
+_i64 = C.c_int64
+
+
+# ------------------------------------------------------------------ C restatement
+def c_softmax(x: torch.Tensor) -> torch.Tensor:
+    y = torch.empty_like(x)
+    fn = lib().oracle_softmax_f16 if x.dtype == torch.float16 else lib().oracle_softmax_f32
+    fn(_p(x), _p(y), _i64(x.shape[0]), _i64(x.shape[1]))
+    return y
+
+
+def c_online_softmax(x: torch.Tensor, block_cols: int) -> torch.Tensor:
+    y = torch.empty_like(x)
+    lib().oracle_online_softmax_f32(_p(x), _p(y), _i64(x.shape[0]), _i64(x.shape[1]), _i64(block_cols))
+    return y
+
+
+def c_layer_norm(x, w, b, eps):
+    y = torch.empty_like(x)
+    mean = torch.empty(x.shape[0], dtype=torch.float32)
+    rstd = torch.empty(x.shape[0], dtype=torch.float32)
+    fn = lib().oracle_layer_norm_f16 if x.dtype == torch.float16 else lib().oracle_layer_norm_f32
+    fn(_p(x), _p(y), _p(w), _p(b), _p(mean), _p(rstd), _i64(x.shape[0]), _i64(x.shape[1]), C.c_float(eps))
+    return y, mean, rstd
+
+
+def c_rms_norm(x, g, eps):
+    y = torch.empty_like(x)
+    fn = lib().oracle_rms_norm_f16 if x.dtype == torch.float16 else lib().oracle_rms_norm_f32
+    fn(_p(x), _p(y), _p(g), _i64(x.shape[0]), _i64(x.shape[1]), C.c_float(eps))
+    return y
+
+
+def c_matmul(a, b, out_dtype=torch.float16, residual=None):
+    M, K = a.shape
+    N = b.shape[1]
+    c = torch.empty(M, N, dtype=out_dtype)
+    if out_dtype == torch.float32:
+        assert residual is None
+        lib().oracle_matmul_f16_f32(_p(a), _p(b), _p(c), _i64(M), _i64(N), _i64(K))
+    else:
+        lib().oracle_matmul_f16_f16(_p(a), _p(b), _p(c), _p(residual) if residual is not None else None,
+                                    _i64(M), _i64(N), _i64(K))
+    return c
+
+
+def c_attention(q, k, v, sm_scale, causal=False, block_n=64):
+    o = torch.empty_like(q)
+    Z, H, N, D = q.shape
+    fn = lib().oracle_attention_f16 if q.dtype == torch.float16 else lib().oracle_attention_f32
+    fn(_p(q), _p(k), _p(v), _p(o), _i64(Z), _i64(H), _i64(N), _i64(D), C.c_float(sm_scale), C.c_int(int(causal)),
+       _i64(block_n))
+    return o
+
+
+def c_attention_unfused(q, k, v, scale, causal=False):
+    Z, H, N, D = q.shape
+    o = torch.empty(q.shape, dtype=torch.float32)
+    lib().oracle_attention_unfused_f16_f32(_p(q), _p(k), _p(v), _p(o), _i64(Z), _i64(H), _i64(N), _i64(D),
+                                           C.c_float(scale), C.c_int(int(causal)))
+    return o
+
+
+def c_silu(x):
+    y = torch.empty_like(x)
+    fn = lib().oracle_silu_f16 if x.dtype == torch.float16 else lib().oracle_silu_f32
+    fn(_p(x), _p(y), _i64(x.numel()))
+    return y
+
+
+def c_swiglu(gu):
+    rows, c2 = gu.shape
+    out = torch.empty(rows, c2 // 2, dtype=torch.float16)
+    lib().oracle_swiglu_f16(_p(gu), _p(out), _i64(rows), _i64(c2 // 2))
+    return out
+
+
+def c_decoder(x, weights, n_heads, head_dim, d_ff, batch, seq, eps):
+    n = len(weights)
+    out = torch.empty_like(x)
+    tabs = []
+    for name in ("wqkv", "wo", "wgu", "wd", "g1", "g2"):
+        tabs.append((C.c_void_p * max(n, 1))(*[w[name].data_ptr() for w in weights]))
+    lib().oracle_decoder_f16(_p(x), _p(out), *tabs, C.c_int(n), C.c_int(n_heads * head_dim), C.c_int(n_heads),
+                             C.c_int(head_dim), C.c_int(d_ff), C.c_int(batch), C.c_int(seq), C.c_float(eps))
+    return out
+
+
+# ------------------------------------------------------------------ torch CPU comparator
+def torch_softmax(x):
+    return F.softmax(x.float(), dim=1).to(x.dtype)
+
+
+def torch_layer_norm(x, w, b, eps):
+    return F.layer_norm(x.float(), (x.shape[1],), weight=w.float(), bias=b.float(), eps=eps).to(x.dtype)
+
+
+def torch_rms_norm(x, g, eps):
+    return F.rms_norm(x.float(), (x.shape[1],), weight=g.float(), eps=eps).to(x.dtype)
+
+
+def torch_matmul(a, b, out_dtype=torch.float16, residual=None):
+    c = torch.matmul(a.float(), b.float())
+    if residual is not None:
+        c = c + residual.float()
+    return c.to(out_dtype)
+
+
+def torch_attention(q, k, v, sm_scale, causal=False):
+    return F.scaled_dot_product_attention(q.float(), k.float(), v.float(), scale=sm_scale,
+                                          is_causal=causal).to(q.dtype)
+
+
+def torch_silu(x):
+    return F.silu(x.float()).to(x.dtype)
+
+
+def torch_decoder(x, weights, n_heads, head_dim, d_ff, batch, seq, eps, store_dtype=torch.float16):
+    """The block stack in plain PyTorch CPU; activations rounded to store_dtype between operators."""
+    d = n_heads * head_dim
+    rd = (lambda t: t.to(store_dtype).float()) if store_dtype is not None else (lambda t: t)
+    cur = x.float().reshape(batch * seq, d)
+    for w in weights:
+        n = rd(F.rms_norm(cur, (d,), weight=w["g1"].float(), eps=eps))
+        qkv = rd(n @ w["wqkv"].float())
+        q, k, v = (qkv[:, i * d:(i + 1) * d].reshape(batch, seq, n_heads, head_dim).transpose(1, 2) for i in range(3))
+        a = rd(F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=1.0 / math.sqrt(head_dim)))
+        a = a.transpose(1, 2).reshape(batch * seq, d)
+        h = rd(a @ w["wo"].float() + cur)
+        n = rd(F.rms_norm(h, (d,), weight=w["g2"].float(), eps=eps))
+        gu = rd(n @ w["wgu"].float())
+        act = rd(F.silu(gu[:, :d_ff]) * gu[:, d_ff:])
+        cur = rd(act @ w["wd"].float() + h)
+    return cur.to(x.dtype).reshape(x.shape)
+
+
+# ------------------------------------------------------------------ seeded inputs of the five configurations
+def _gen(seed):
+    return torch.Generator(device="cpu").manual_seed(seed)
+
+
+def make_softmax_inputs(rows=8192, cols=1024, dtype=torch.float32, seed=1001):
+    return torch.randn(rows, cols, generator=_gen(seed)).to(dtype)
+
+
+def make_layer_norm_inputs(rows=16384, cols=4096, dtype=torch.float16, seed=1002):
+    g = _gen(seed)
+    x = torch.randn(rows, cols, generator=g).to(dtype)
+    w = (0.5 + torch.rand(cols, generator=g)).to(dtype)
+    b = (-0.1 + 0.2 * torch.rand(cols, generator=g)).to(dtype)
+    return x, w, b
+
+
+def make_matmul_inputs(M=4096, N=4096, K=4096, seed=1003):
+    g = _gen(seed)
+    a = (2 * torch.rand(M, K, generator=g) - 1).to(torch.float16)
+    b = (2 * torch.rand(K, N, generator=g) - 1).to(torch.float16)
+    return a, b
+
+
+def make_attention_inputs(Z=4, H=32, N=4096, D=128, dtype=torch.float16, seed=1004):
+    g = _gen(seed)
+    s = D ** -0.5
+    return tuple((torch.randn(Z, H, N, D, generator=g) * s).to(dtype) for _ in range(3))
+
+
+def make_decoder_inputs(n_layers=4, d_model=2048, n_heads=16, d_ff=8192, batch=8, seq=1024, seed=1005):
+    g = _gen(seed)
+    x = (0.02 * torch.randn(batch, seq, d_model, generator=g)).to(torch.float16)
+    weights = []
+    for layer in range(n_layers):
+        gl = _gen(seed + 1 + layer)
+        mk = lambda r, c: (torch.randn(r, c, generator=gl) * r ** -0.5).to(torch.float16)
+        weights.append({
+            "wqkv": mk(d_model, 3 * d_model), "wo": mk(d_model, d_model), "wgu": mk(d_model, 2 * d_ff),
+            "wd": mk(d_ff, d_model), "g1": torch.ones(d_model, dtype=torch.float16),
+            "g2": torch.ones(d_model, dtype=torch.float16),
+        })
+    return x, weights
+
+
+def max_rel_err(got: torch.Tensor, ref: torch.Tensor) -> float:
+    """max |got - ref| / max |ref|: the relative error the tolerances of the benchmark are stated in."""
+    ref = ref.float()
+    denom = ref.abs().max().clamp_min(1e-30)
+    return float((got.float() - ref).abs().max() / denom)

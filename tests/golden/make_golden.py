@@ -1,0 +1,136 @@
+"""Generates the golden fixtures in this directory from the reference's own Triton kernels.
+
+Runs only where the reference checkout is present (default /root/reference, or $HEXAGON_MLIR_REF).
+The reference's test modules are imported unmodified with
+
+  * TRITON_INTERPRET=1, so the @triton.jit kernels execute in Triton's NumPy interpreter on CPU,
+  * a stub ``triton.backends.qcom_hexagon_backend.driver.HexagonDriver`` and a no-op
+    ``triton.runtime.driver.set_active`` (the real ones need the Hexagon toolchain),
+  * ``parameterize_func_name`` (a rename of the kernel per dtype) made the identity, because the
+    interpreter finds the kernel by its source name,
+  * ``torch.rand`` seeded and recorded, and ``torch.allclose`` wrapped to capture the kernel's
+    output and the torch reference the test compares it with.
+
+Each fixture ``<case>.npz`` holds the recorded inputs (in0, in1, ...), ``output`` (what the
+reference kernel produced) and ``expected`` (the torch value the reference test asserted against).
+Usage: ``python tests/golden/make_golden.py``.
+"""
+import importlib
+import os
+import sys
+import types
+from pathlib import Path
+
+os.environ["TRITON_INTERPRET"] = "1"
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import triton  # noqa: E402
+
+REF = Path(os.environ.get("HEXAGON_MLIR_REF", "/root/reference"))
+OUT = Path(__file__).resolve().parent
+
+
+def _stub_backend():
+    pkg = types.ModuleType("triton.backends.qcom_hexagon_backend")
+    drv = types.ModuleType("triton.backends.qcom_hexagon_backend.driver")
+
+    class HexagonDriver:  # the tests only construct it
+        pass
+
+    drv.HexagonDriver = HexagonDriver
+    sys.modules[pkg.__name__] = pkg
+    sys.modules[drv.__name__] = drv
+    triton.runtime.driver.set_active = lambda *_a, **_k: None
+
+
+class Recorder:
+    """Records torch.rand results and the operands of torch.allclose while a reference test runs."""
+
+    def __init__(self, seed):
+        self.inputs, self.output, self.expected = [], None, None
+        self.seed = seed
+
+    def __enter__(self):
+        self._rand, self._allclose = torch.rand, torch.allclose
+        torch.manual_seed(self.seed)
+
+        def rand(*a, **k):
+            t = self._rand(*a, **k)
+            self.inputs.append(t.clone())
+            return t
+
+        def allclose(a, b, *rest, **k):
+            self.output, self.expected = a.clone(), b.clone()
+            return self._allclose(a, b, *rest, **k)
+
+        torch.rand, torch.allclose = rand, allclose
+        return self
+
+    def __exit__(self, *exc):
+        torch.rand, torch.allclose = self._rand, self._allclose
+
+    def save(self, name):
+        arrays = {f"in{i}": t.numpy() for i, t in enumerate(self.inputs)}
+        arrays["output"] = self.output.numpy()
+        arrays["expected"] = self.expected.numpy()
+        np.savez_compressed(OUT / f"{name}.npz", **arrays)
+        err = float((self.output.float() - self.expected.float()).abs().max())
+        print(f"{name}: {len(self.inputs)} inputs, output {tuple(self.output.shape)} {self.output.dtype}, "
+              f"max |kernel - torch| = {err:.3e}")
+
+
+def main():
+    if not REF.exists():
+        raise SystemExit(f"{REF} not found: fixtures can only be regenerated next to the reference checkout")
+    _stub_backend()
+    sys.path.insert(0, str(REF / "test"))
+    # The interpreter re-parses the kernel source and looks the function up by its source name, so
+    # the dtype suffix that parameterize_func_name appends to __name__ is left out here; the
+    # suffix only renames the kernel.
+    pkg = importlib.import_module("python")
+    pkg.parameterize_func_name = lambda *_p: (lambda f: f)
+    mod = lambda n: importlib.import_module(f"python.triton.{n}")
+
+    sm = mod("test_softmax")
+    for dt, tag in ((torch.float32, "f32"), (torch.float16, "f16")):
+        with Recorder(11) as r:
+            sm.test_softmax(dt)
+        r.save(f"softmax_128x128_{tag}")
+
+    osm = mod("test_online_softmax")
+    with Recorder(12) as r:
+        osm.test_online_softmax(4)
+    r.save("online_softmax_128x128_f32")
+
+    ln = mod("test_layer_norm")
+    with Recorder(13) as r:
+        ln.test_layer_norm(1024, 4, torch.float32)
+    r.save("layer_norm_27x1024_f32")
+
+    rn = mod("test_rms_norm")
+    for dt, tag in ((torch.float32, "f32"), (torch.float16, "f16")):
+        with Recorder(14) as r:
+            rn.test_rms_norm(4, dt)
+        r.save(f"rms_norm_{rn.NUM_ROWS}x{rn.NUM_COLS}_{tag}")
+
+    mm = mod("test_matmul")
+    with Recorder(15) as r:
+        mm.test_matmul(256, 128, 64)
+    r.save("matmul_256x128x64_f16")
+
+    fa = mod("test_flash_attention")
+    fa.N_CTX, fa.BLOCK_M = 256, 64  # module-level shape constants of the test; same kernel, smaller tensors
+    fa.stride_0, fa.stride_1 = fa.H * 256 * fa.D_HEAD, 256 * fa.D_HEAD
+    with Recorder(16) as r:
+        fa.test_flash_attention()
+    r.save("flash_attention_1x1x256x64_f32")
+
+    si = mod("test_silu")
+    for dt, tag in ((torch.float32, "f32"), (torch.float16, "f16")):
+        with Recorder(17) as r:
+            si.test_silu(16384, 4, dt, False, False)
+        r.save(f"silu_16384_{tag}")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,112 @@
+"""CPU: pins the oracle against the fixtures produced by the reference's own Triton kernels
+(tests/golden/make_golden.py) and against the torch values the reference tests assert against.
+Tolerances are the reference tests' own (softmax atol 1e-5 / 1e-3, layer norm 1e-5, rms norm 1e-2,
+matmul 0.2, flash attention allclose defaults, silu 1e-2)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+
+def load(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    return {k: torch.from_numpy(z[k]) for k in z.files}
+
+
+@pytest.mark.parametrize("tag,atol", [("f32", 1e-5), ("f16", 1e-3)])
+def test_softmax_golden(golden_dir, tag, atol):
+    g = load(golden_dir, f"softmax_128x128_{tag}")
+    x = g["in0"]
+    for got in (O.c_softmax(x), O.torch_softmax(x)):
+        assert torch.allclose(got, g["output"], atol=atol)
+        assert torch.allclose(got, g["expected"], atol=atol)
+
+
+def test_online_softmax_golden(golden_dir):
+    g = load(golden_dir, "online_softmax_128x128_f32")
+    got = O.c_online_softmax(g["in0"], 32)
+    assert torch.allclose(got, g["output"], atol=1e-5)
+    assert torch.allclose(got, g["expected"], atol=1e-5)
+
+
+def test_layer_norm_golden(golden_dir):
+    g = load(golden_dir, "layer_norm_27x1024_f32")
+    x, w, b = g["in0"], g["in1"], g["in2"]
+    y, mean, rstd = O.c_layer_norm(x, w, b, 1e-5)
+    assert torch.allclose(y, g["output"], atol=1e-5)
+    assert torch.allclose(y, g["expected"], atol=1e-5)
+    assert torch.allclose(O.torch_layer_norm(x, w, b, 1e-5), g["output"], atol=1e-5)
+    assert torch.allclose(mean, x.mean(dim=1), atol=1e-6)
+    assert torch.allclose(rstd, 1.0 / torch.sqrt(x.var(dim=1, unbiased=False) + 1e-5), rtol=1e-5)
+
+
+@pytest.mark.parametrize("tag", ["f32", "f16"])
+def test_rms_norm_golden(golden_dir, tag):
+    g = load(golden_dir, f"rms_norm_127x513_{tag}")
+    x, w = g["in0"], g["in1"]
+    eps = 1e-5
+    for got in (O.c_rms_norm(x, w, eps), O.torch_rms_norm(x, w, eps)):
+        assert torch.allclose(got, g["output"], atol=1e-2)
+        assert torch.allclose(got, g["expected"], atol=1e-2)
+
+
+def test_matmul_golden(golden_dir):
+    g = load(golden_dir, "matmul_256x128x64_f16")
+    a, b = g["in0"], g["in1"]
+    for got in (O.c_matmul(a, b, torch.float16), O.torch_matmul(a, b, torch.float16)):
+        assert torch.allclose(got, g["output"], atol=2e-1)
+        assert torch.allclose(got, g["expected"], atol=2e-1)
+        assert O.max_rel_err(got, g["output"]) < 2e-3  # one fp16 rounding apart at most
+    c32 = O.c_matmul(a, b, torch.float32)
+    assert torch.allclose(c32, a.float() @ b.float(), rtol=1e-5, atol=1e-5)
+
+
+def test_flash_attention_golden(golden_dir):
+    g = load(golden_dir, "flash_attention_1x1x256x64_f32")
+    q, k, v = g["in0"], g["in1"], g["in2"]
+    got = O.c_attention(q, k, v, 0.5, causal=False, block_n=64)
+    assert torch.allclose(got, g["output"], rtol=1e-5, atol=1e-6)
+    assert torch.allclose(got, g["expected"], rtol=1e-5, atol=1e-6)
+    assert torch.allclose(O.torch_attention(q, k, v, 0.5), g["output"], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("tag", ["f32", "f16"])
+def test_silu_golden(golden_dir, tag):
+    g = load(golden_dir, f"silu_16384_{tag}")
+    x = g["in0"]
+    for got in (O.c_silu(x), O.torch_silu(x)):
+        assert torch.allclose(got, g["output"], atol=1e-2)
+        assert torch.allclose(got, g["expected"], atol=1e-2)
+
+
+def test_known_constants():
+    # constants the reference's lowered IR carries (SDPA.mlir:18, hexkl_attention/input.mlir:6)
+    assert abs(8 ** -0.5 - 0.353553385) < 1e-8
+    assert abs(0.5 * 1.44269504 - 0.72134751) < 1e-7
+
+
+def test_c_oracle_matches_torch_on_config_shapes():
+    torch.manual_seed(0)
+    x = O.make_softmax_inputs(64, 1024)
+    assert torch.allclose(O.c_softmax(x), O.torch_softmax(x), atol=1e-6)
+    x, w, b = O.make_layer_norm_inputs(32, 4096)
+    y, _, _ = O.c_layer_norm(x, w, b, 1e-5)
+    assert O.max_rel_err(y, O.torch_layer_norm(x, w, b, 1e-5)) < 2e-3
+    a, bm = O.make_matmul_inputs(64, 96, 128)
+    assert O.max_rel_err(O.c_matmul(a, bm), O.torch_matmul(a, bm)) < 2e-3
+    q, k, v = O.make_attention_inputs(1, 2, 256, 128)
+    for causal in (False, True):
+        got = O.c_attention(q, k, v, 128 ** -0.5, causal)
+        assert O.max_rel_err(got, O.torch_attention(q, k, v, 128 ** -0.5, causal)) < 2e-2
+        unf = O.c_attention_unfused(q, k, v, 128 ** -0.5, causal)
+        assert O.max_rel_err(unf, O.torch_attention(q.float(), k.float(), v.float(), 128 ** -0.5, causal)) < 1e-4
+
+
+def test_decoder_oracles_agree():
+    x, ws = O.make_decoder_inputs(2, 256, 2, 512, 2, 128)
+    c = O.c_decoder(x.reshape(-1, 256), ws, 2, 128, 512, 2, 128, 1e-6).reshape(x.shape)
+    t = O.torch_decoder(x, ws, 2, 128, 512, 2, 128, 1e-6)
+    assert O.max_rel_err(c, t) < 2e-2
