@@ -1,0 +1,186 @@
+"""CPU: the host-side mirror of the reference's launcher interface -- option filtering, argument
+binding by the reference kernels' parameter names, name-based dispatch, the triton shim -- and the
+multi-GPU partition/gather logic on two gloo ranks."""
+import os
+import socket
+import sys
+import warnings
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import hexb200
+from hexb200 import kernels, options
+from hexb200.dist import all_gather_rows, shard_range, shard_rows
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_split_options_accepts_every_reference_flag():
+    kw = {"NUM_ROWS": 4, "enableVTCMTiling": False, "enableHexKL": True, "iterations": 1, "scratch": 0,
+          "num_threads": 4, "hexKLMode": "macro"}
+    args, opts = options.split_options(kw, ["x_ptr", "NUM_ROWS"])
+    assert args == {"NUM_ROWS": 4}
+    assert set(opts) == set(kw) - {"NUM_ROWS"}
+
+
+def test_split_options_warns_on_option_like_typos_and_rejects_unknowns():
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        args, opts = options.split_options({"enableTurbo": True, "my_scratch": 1}, [])
+        assert not args and not opts
+        assert any("Unsupported runtime options ignored" in str(x.message) for x in w)
+    with pytest.raises(TypeError):
+        options.split_options({"bogus": 1}, [])
+    with pytest.raises(ValueError):
+        options.split_options({"target_artifact": "exe"}, [])
+
+
+def test_option_field_list_matches_the_reference_dataclass():
+    ref = "/root/reference/qcom_hexagon_backend/backend/hexagon_options.py"
+    if not os.path.exists(ref):
+        pytest.skip("reference checkout not present")
+    import re
+
+    fields = set(re.findall(r"^    (\w+): [\w\[\], \.]+ =", open(ref).read(), flags=re.M))
+    assert fields == set(options.HEXAGON_OPTION_FIELDS)
+
+
+def test_lookup_strips_the_dtype_suffix():
+    assert kernels.lookup("softmax_kernel_float16").name == "softmax_kernel"
+    assert kernels.lookup("layer_norm_fwd_kernel_float32").name == "layer_norm_fwd_kernel"
+    assert kernels.lookup("matmul").name == "matmul"
+    with pytest.raises(NotImplementedError):
+        kernels.lookup("conv2d_kernel")
+
+
+def test_launcher_binds_by_reference_parameter_names(monkeypatch):
+    seen = {}
+    monkeypatch.setattr(kernels.ops, "softmax", lambda x, out: seen.update(x=x, out=out))
+    x, out = torch.zeros(4, 8), torch.zeros(4, 8)
+    kernels.lookup("softmax_kernel_float32")[(4,)](x, out, NUM_ROWS=4, NUM_COLS=8, BLOCK_SIZE=8,
+                                                   enableMultiThreading=False, enableHVXInlining=True)
+    assert seen["x"] is x and seen["out"] is out
+    with pytest.raises(TypeError):
+        kernels.softmax_kernel[(1,)](x, out, NUM_ROWS=4)                     # NUM_COLS missing
+
+    monkeypatch.setattr(kernels.ops, "layer_norm",
+                        lambda x, y, w, b, mean, rstd, eps: seen.update(eps=eps, shape=tuple(x.shape)))
+    flat = torch.zeros(27 * 16)
+    kernels.layer_norm_fwd_kernel[(1,)](flat, flat.clone(), torch.zeros(16), torch.zeros(16), torch.zeros(27),
+                                        torch.zeros(27), EPSILON=1e-5, NUM_ROWS=27, NUM_COLS=16, BLOCK_SIZE=16)
+    assert seen["eps"] == 1e-5 and seen["shape"] == (27, 16)
+
+
+def test_attention_launcher_selects_the_head_of_pid1(monkeypatch):
+    calls = []
+
+    def fake(q, k, v, o, sm_scale, causal):
+        calls.append((q.clone(), causal))
+        o.copy_(q)
+
+    monkeypatch.setattr(kernels.ops, "attention", fake)
+    Z, H, N, D = 2, 3, 8, 4
+    q = torch.arange(Z * H * N * D, dtype=torch.float32).reshape(Z, H, N, D)
+    out = torch.zeros_like(q)
+    kernels.attention_fwd_kernel[(4,)](pid1=4, Q=q, K=q, V=q, sm_scale=0.5, Out=out, H=H, N_CTX=N, BLOCK_M=2,
+                                       BLOCK_DMODEL=D, BLOCK_N=2, STAGE=1, stride_0=H * N * D, stride_1=N * D,
+                                       stride_2=D, stride_3=1, enableHexKL=False)
+    z, h = divmod(4, H)
+    assert torch.equal(calls[0][0][0, 0], q[z, h]) and calls[0][1] is False
+    assert torch.equal(out[z, h], q[z, h]) and out.sum() == q[z, h].sum()      # only that head was written
+
+
+def test_triton_shim_routes_jit_kernels_by_name(monkeypatch):
+    from hexb200 import triton_shim
+
+    triton = triton_shim.install()
+    from triton.backends.qcom_hexagon_backend.driver import HexagonDriver
+
+    triton.runtime.driver.set_active(HexagonDriver())
+    seen = {}
+    monkeypatch.setattr(kernels.ops, "rms_norm", lambda x, y, w, eps: seen.update(eps=eps))
+
+    @triton.jit
+    def rms_norm_fwd_kernel(x_ptr, y_ptr, weights_ptr, BLOCK_SIZE, EPSILON, NUM_COLS, NUM_ROWS):
+        raise AssertionError("the body of a jit function is never executed")
+
+    rms_norm_fwd_kernel.__name__ = "rms_norm_fwd_kernel_float16"
+    x = torch.zeros(3, 8)
+    rms_norm_fwd_kernel[(4,)](x, x.clone(), torch.ones(8), EPSILON=1e-5, NUM_ROWS=3, NUM_COLS=8, BLOCK_SIZE=8,
+                              enableHexagonmemCopyToDMA=True)
+    assert seen["eps"] == 1e-5
+
+    @triton.jit
+    def _max(a, b):
+        return a
+
+    with pytest.raises(NotImplementedError):
+        _max[(1,)](1, 2)
+
+
+def test_host_tensors_reach_the_library_and_fail_loudly_without_a_gpu():
+    if torch.cuda.is_available():
+        pytest.skip("this check is for the GPU-less box")
+    x = torch.rand(4, 8)
+    with pytest.raises(hexb200.HexbError) as e:
+        kernels.softmax_kernel[(1,)](x, torch.empty_like(x), NUM_ROWS=4, NUM_COLS=8, BLOCK_SIZE=8)
+    assert e.value.status_name in ("HEXB_ERR_CUDA", "HEXB_ERR_NO_DEVICE")
+
+
+def test_shard_range_covers_every_unit_once():
+    for n in (0, 1, 7, 8, 128, 16384, 1001):
+        for world in (1, 2, 3, 4, 8):
+            spans = [shard_range(n, world, r) for r in range(world)]
+            assert sum(c for _, c in spans) == n
+            pos = 0
+            for s, c in spans:
+                assert s == pos
+                pos += c
+            counts = [c for _, c in spans]
+            assert max(counts) - min(counts) <= 1
+    with pytest.raises(ValueError):
+        shard_range(4, 2, 2)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _rank_main(rank, world, port, rows, cols, q):
+    sys.path.insert(0, ROOT)
+    from oracle import oracle as O
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        x = O.make_softmax_inputs(rows, cols, seed=77)            # every rank draws the same matrix
+        mine = shard_rows(x, world, rank)
+        y_local = O.torch_softmax(mine)                           # stand-in for the per-GPU kernel
+        y = all_gather_rows(y_local, rows)
+        ok = torch.allclose(y, O.torch_softmax(x), atol=1e-7)
+        q.put((rank, bool(ok), tuple(y.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("rows", [64, 37])
+def test_two_rank_shard_and_gather_gloo(rows):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, rows, 32, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok, _ in res)
+    assert all(shape == (rows, 32) for _, _, shape in res)
