@@ -60,6 +60,7 @@ PROTOTYPES = {
     "hexb_swiglu_f16": (_i, [_vp, _vp, _i64, _i64, _vp]),
     "hexb_decoder_workspace_bytes": (C.c_size_t, [C.POINTER(DecoderConfig)]),
     "hexb_decoder_forward_f16": (_i, [C.POINTER(DecoderConfig), C.POINTER(DecoderWeights), _vp, _vp, _vp, C.c_size_t, _vp]),
+    "hexb_decoder_forward_f16_noalloc": (_i, [C.POINTER(DecoderConfig), C.POINTER(DecoderWeights), _vp, _vp, _vp]),
     "hexb_softmax_host": (_i, [_i, _vp, _vp, _i64, _i64]),
     "hexb_layer_norm_host": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f]),
     "hexb_rms_norm_host": (_i, [_i, _vp, _vp, _vp, _i64, _i64, _f]),

@@ -12,6 +12,8 @@
 // Heads are split and merged by strides inside the attention call (q|k|v column blocks of the
 // QKV product, head-major inside each block); no transposes.  The residual adds ride in the
 // epilogue of the Wo and Wd products.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace hexb {
@@ -91,4 +93,41 @@ extern "C" int hexb_decoder_forward_f16(const hexb_decoder_config *cfg, const he
     xin = xout;
   }
   return HEXB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant.  The workspace of hexb_decoder_forward_f16 is replaced by a fixed array
+// in the library image, for hosts that cannot call cudaMalloc at this point (all device memory
+// already handed to their own pool, or a latency budget that rules out an allocation).
+//
+// In host code `g_decoder_scratch` is only a handle for the symbol, not a device address: its
+// address is fetched once per device with cudaGetSymbolAddress while that device is current, and
+// that pointer is what the kernels receive.  The array is shared by every call on the device and
+// keeps the previous call's contents; the block stack writes each intermediate before reading it,
+// so no clearing is needed, but overlapping calls on one device would race on it.
+static __device__ __align__(256) unsigned char g_decoder_scratch[HEXB_DECODER_STATIC_SCRATCH_BYTES];
+
+extern "C" int hexb_decoder_forward_f16_noalloc(const hexb_decoder_config *cfg,
+                                                const hexb_decoder_weights *w, const void *x,
+                                                void *out, void *stream) {
+  using namespace hexb;
+  static void *scratch_ptr[64] = {};
+  static std::mutex mu;
+  DecoderPlan p;
+  if (int s = decoder_plan(cfg, &p)) return s;
+  if (p.total > (size_t)HEXB_DECODER_STATIC_SCRATCH_BYTES) return HEXB_ERR_WORKSPACE;  // beyond the fixed array
+  int dev = -1;
+  HEXB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return HEXB_ERR_NO_DEVICE;
+  void *ptr = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!scratch_ptr[dev]) {
+      void *sym = nullptr;
+      HEXB_CUDA_OK(cudaGetSymbolAddress((void **)&sym, g_decoder_scratch));  // device `dev` is current
+      scratch_ptr[dev] = sym;
+    }
+    ptr = scratch_ptr[dev];
+  }
+  return hexb_decoder_forward_f16(cfg, w, x, out, ptr, (size_t)HEXB_DECODER_STATIC_SCRATCH_BYTES, stream);
 }

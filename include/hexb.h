@@ -140,6 +140,27 @@ int hexb_decoder_forward_f16(const hexb_decoder_config *cfg, const hexb_decoder_
                              const void *x, void *out, void *workspace, size_t workspace_bytes,
                              void *stream);
 
+/* ---- decoder forward for callers that must not allocate.  No counterpart in the reference.
+ * Same computation and arguments as hexb_decoder_forward_f16, minus the workspace pair: the
+ * intermediate activations live in a fixed HEXB_DECODER_STATIC_SCRATCH_BYTES array that is part of
+ * the library image on every GPU that loads it (held until the process exits).  It is meant for
+ * hosts that hand all device memory to their own pool at start-up, or that sit in a serving loop
+ * where a cudaMalloc -- which may fail, fragment, or synchronise the device -- is not acceptable:
+ * this call never calls cudaMalloc, cudaFree or any allocating library routine.
+ *   - A configuration whose hexb_decoder_workspace_bytes() exceeds the array is refused with
+ *     HEXB_ERR_WORKSPACE and nothing is launched (64 MiB: e.g. 862 tokens at d_model 2048 /
+ *     d_ff 8192, or 10082 tokens at d_model 256 / d_ff 512).
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *     with that device current) and caches it; make that first call before starting any stream
+ *     capture.
+ *   - All calls on a device share the one array.  It keeps whatever the previous call left there;
+ *     the block stack writes every intermediate before reading it, so nothing has to be cleared.
+ *     Two calls that overlap on the GPU (different streams, or different host threads) race on
+ *     the array: serialise them. */
+#define HEXB_DECODER_STATIC_SCRATCH_BYTES (64u << 20)
+int hexb_decoder_forward_f16_noalloc(const hexb_decoder_config *cfg, const hexb_decoder_weights *w,
+                                     const void *x, void *out, void *stream);
+
 /* ---- host-buffer entry points (the launcher path).  Replace the generated wrapper main() that
  * loads `<kernel>_t{i}.raw`, runs the kernel and dumps `<kernel>_o{i}.raw`
  * (qcom_hexagon_backend/backend/triton_hexagon_launcher.py:111-123,

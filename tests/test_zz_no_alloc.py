@@ -1,0 +1,58 @@
+"""GPU: the allocation-free decoder entry point (hexb_decoder_forward_f16_noalloc).
+
+Some hosts cannot call cudaMalloc when they need a forward pass: they gave all device memory to
+their own pool at start-up, or they run a serving loop whose latency budget has no room for an
+allocation.  For them the library carries its intermediate activations in a fixed 64 MiB array
+inside the library image.  This test calls that entry point through the C ABI twice in a row with
+different inputs (the array is shared and keeps the first call's contents, so the second call shows
+that stale contents do not leak into the result) and compares each output with the workspace-taking
+entry point on the same inputs, within the fp16 tolerance of the other GPU tests; it also checks
+that a configuration beyond the fixed array is refused with HEXB_ERR_WORKSPACE.
+The file name sorts last so that a run stopping at the first failure has already run every other test.
+"""
+import ctypes as C
+
+import pytest
+import torch
+
+import hexb200
+from hexb200 import _lib, ops
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+REL_F16 = 2e-2
+
+
+def test_noalloc_decoder_matches_workspace_entry_point_twice():
+    assert torch.cuda.is_available()
+    lib = hexb200.load()
+    dev = torch.device("cuda:0")
+    L, d, H, f, B, S = 2, 256, 2, 512, 2, 128
+    x1, ws = O.make_decoder_inputs(L, d, H, f, B, S, seed=2001)
+    x2, _ = O.make_decoder_inputs(L, d, H, f, B, S, seed=2002)
+    wd = [{k: v.to(dev) for k, v in w.items()} for w in ws]
+    stack = ops.DecoderStack(wd, H, d // H, f, B, S, 1e-6)          # owns the weight pointer tables
+    assert stack.ws_bytes <= (64 << 20)
+    stream = torch.cuda.current_stream().cuda_stream
+    for x in (x1, x2):                                              # two calls in a row, shared array
+        xd = x.to(dev)
+        want = torch.empty_like(xd)
+        stack.forward(xd, want)                                     # existing entry point, explicit workspace
+        got = torch.full_like(xd, float("nan"))
+        st = lib.hexb_decoder_forward_f16_noalloc(C.byref(stack.cfg), C.byref(stack.cweights), xd.data_ptr(),
+                                                  got.data_ptr(), stream)
+        assert st == 0, lib.hexb_status_string(st)
+        torch.cuda.synchronize()
+        assert hexb200.device_status() == 0
+        assert torch.isfinite(got).all()
+        assert O.max_rel_err(got.cpu(), want.cpu()) < REL_F16
+        assert O.max_rel_err(got.cpu(), O.torch_decoder(x, ws, H, d // H, f, B, S, 1e-6)) < REL_F16
+
+
+def test_noalloc_decoder_refuses_sizes_beyond_the_fixed_array():
+    lib = hexb200.load()
+    big = _lib.DecoderConfig(4, 2048, 16, 128, 8192, 8, 1024, 1e-6)   # needs ~608 MiB of intermediates
+    assert lib.hexb_decoder_workspace_bytes(C.byref(big)) > (64 << 20)
+    st = lib.hexb_decoder_forward_f16_noalloc(C.byref(big), None, None, None, None)
+    assert lib.hexb_status_string(st).decode() == "HEXB_ERR_WORKSPACE"
