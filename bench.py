@@ -277,23 +277,42 @@ WORKLOADS = {"layernorm": LayerNormWL, "softmax": SoftmaxWL, "gemm": GemmWL, "at
              "decoder": DecoderWL}
 
 
-def time_steps(wl, steps, warmup, barrier):
-    """W untimed steps, then exactly K steps between two CUDA events on the launching stream."""
+def time_steps(wl, steps, warmup, barrier, use_graph=True):
+    """W untimed steps, then exactly K steps between two CUDA events on the launching stream.
+
+    The K steps are captured once into a CUDA graph (the library's launches are plain stream
+    launches, so they capture) and the timed region is one replay of it: the same K kernel
+    launches, without the Python and driver launch gap between them.  Falls back to K eager calls
+    if capture is refused.  Returns (ms for K steps, t0, t1, mode)."""
     for i in range(warmup):
         wl.step(i)
+    torch.cuda.synchronize()
+    graph = None
+    if use_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(steps):
+                    wl.step(warmup + i)
+            graph.replay()  # untimed: uploads the graph
+        except Exception:
+            graph = None
     torch.cuda.synchronize()
     barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e0.record()
-    for i in range(steps):
-        wl.step(warmup + i)
+    if graph is not None:
+        graph.replay()
+    else:
+        for i in range(steps):
+            wl.step(warmup + i)
     e1.record()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
     barrier()
-    return e0.elapsed_time(e1), t0, t1
+    return e0.elapsed_time(e1), t0, t1, ("cuda_graph" if graph is not None else "eager")
 
 
 def roofline(wl, ms_per_step, peaks):
@@ -319,10 +338,10 @@ def cpu_reference_step(name):
     from oracle import oracle as O
 
     if name == "layernorm":
-        rows = 2048
+        rows = 16384  # the full workload: a smaller sample would sit in the CPU's caches
         x, w, b = O.make_layer_norm_inputs(rows, 4096)
         return (lambda: F.layer_norm(x, (4096,), weight=w, bias=b, eps=1e-5), 2 * rows * 4096 * 2 + 4 * 4096,
-                f"{rows} of 16384 rows, F.layer_norm fp16 on CPU")
+                "full [16384 x 4096] fp16, F.layer_norm on CPU")
     if name == "softmax":
         x = O.make_softmax_inputs(8192, 1024)
         return (lambda: F.softmax(x, dim=1), 2 * 8192 * 1024 * 4, "full [8192 x 1024] fp32, F.softmax on CPU")
@@ -442,6 +461,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="layernorm", choices=sorted(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the other four configurations and the CPU baseline")
+    ap.add_argument("--eager", action="store_true", help="time K eager launches instead of one CUDA-graph replay of them")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement (profiling runs)")
     ap.add_argument("--gather", action="store_true", help="also time the all-gather of output shards (N > 1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -487,7 +508,7 @@ def main():
     wl = WORKLOADS[args.workload](dev)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    ms_total, t0, t1 = time_steps(wl, args.steps, args.warmup, barrier)
+    ms_total, t0, t1, launch_mode = time_steps(wl, args.steps, args.warmup, barrier, not args.eager)
     sampler.stop()
     clocks = sampler.summary(t0, t1)
     if dist:
@@ -522,10 +543,14 @@ def main():
                 "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": cfg,
                 "roofline": roofline(wl, ms_per_step, peaks), "clocks": clocks,
-                "gpu_launches": args.steps * wl.launches_per_step, "device_status": status}
+                "gpu_launches": args.steps * wl.launches_per_step, "launch_mode": launch_mode,
+                "device_status": status}
         if gather:
             line["gather"] = gather
-        line["e2e"] = e2e_layernorm(wl, args.steps) if wl.name == "layernorm" else e2e_generic(wl, args.steps)
+        if args.no_e2e:
+            line["e2e"] = None
+        else:
+            line["e2e"] = e2e_layernorm(wl, args.steps) if wl.name == "layernorm" else e2e_generic(wl, args.steps)
 
     if rank == 0 and world == 1 and not args.no_extras:
         del wl
@@ -536,7 +561,7 @@ def main():
                 continue
             w2 = WORKLOADS[name](dev)
             k2 = {"softmax": 200, "gemm": 50, "attention": 10, "decoder": 5}.get(name, 20)
-            ms2, _, _ = time_steps(w2, k2, 3, lambda: None)
+            ms2, _, _, _ = time_steps(w2, k2, 3, lambda: None, not args.eager)
             ms2 /= k2
             sc = 1e9 if w2.bound == "hbm" else 1e12
             extras[name] = {"value": round(w2.work_per_step() / (ms2 * 1e-3) / sc, 2), "unit": w2.unit,

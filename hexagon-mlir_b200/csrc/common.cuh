@@ -101,6 +101,15 @@ __device__ __forceinline__ void st_stream16(void *p, uint4 v) {
                "r"(v.z), "r"(v.w)
                : "memory");
 }
+// Makes the compiler forget what it knows about a packed 16-byte register vector, so that a later
+// unpack is re-materialised from the packed form instead of keeping every unpacked float alive.
+__device__ __forceinline__ void opaque(uint4 &v) {
+  asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w));
+}
+__device__ __forceinline__ void opaque(float4 &v) {
+  asm volatile("" : "+f"(v.x), "+f"(v.y), "+f"(v.z), "+f"(v.w));
+}
+
 template <typename R>
 __device__ __forceinline__ R ld_stream_as(const void *p) {
   uint4 v = ld_stream16(p);

@@ -9,6 +9,7 @@
 // The row lives in registers between the statistics and the normalisation, so HBM is touched once
 // each way; the two reduction passes of the reference run over registers, not memory.  Gains and
 // biases are loaded once per thread and reused for every row the thread's CTA walks.
+#include "rowring.cuh"
 #include "rowwise.cuh"
 
 namespace hexb {
@@ -100,6 +101,258 @@ norm_rows_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict
   }
 }
 
+
+// ---- fp16 fast path of the ring kernel: the row, gains and biases stay packed (two fp16 per
+// register).  Statistics accumulate in fp32 straight from the fp16 operands with the sm_100
+// mixed-precision add / sub / fma (no separate conversion); the normalised value
+// (x - mean) * rstd is formed in fp32, rounded to fp16 and the affine step runs as one packed
+// fp16 fma per pair.
+__device__ __forceinline__ void h2_sum(uint32_t w, float &s) {
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\t"
+      "add.rn.f32.f16 %0, lo, %0;\n\tadd.rn.f32.f16 %0, hi, %0;\n\t}"
+      : "+f"(s) : "r"(w));
+}
+__device__ __forceinline__ void h2_sumsq(uint32_t w, float &q) {
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\t"
+      "fma.rn.f32.f16 %0, lo, lo, %0;\n\tfma.rn.f32.f16 %0, hi, hi, %0;\n\t}"
+      : "+f"(q) : "r"(w));
+}
+__device__ __forceinline__ void h2_centred_sumsq(uint32_t w, float mean, float &q) {
+  asm("{\n\t.reg .b16 lo, hi;\n\t.reg .f32 d0, d1;\n\tmov.b32 {lo, hi}, %1;\n\t"
+      "sub.rn.f32.f16 d0, lo, %2;\n\tsub.rn.f32.f16 d1, hi, %2;\n\t"
+      "fma.rn.f32 %0, d0, d0, %0;\n\tfma.rn.f32 %0, d1, d1, %0;\n\t}"
+      : "+f"(q) : "r"(w), "f"(mean));
+}
+// ((x - mean) * rstd) -> fp16 pair, then * g + b in packed fp16.
+__device__ __forceinline__ uint32_t h2_norm_affine(uint32_t w, float mean, float rstd, uint32_t g, uint32_t b) {
+  uint32_t out;
+  asm("{\n\t.reg .b16 lo, hi;\n\t.reg .f32 d0, d1;\n\t.reg .b32 t;\n\tmov.b32 {lo, hi}, %1;\n\t"
+      "sub.rn.f32.f16 d0, lo, %2;\n\tsub.rn.f32.f16 d1, hi, %2;\n\t"
+      "mul.rn.f32 d0, d0, %3;\n\tmul.rn.f32 d1, d1, %3;\n\t"
+      "cvt.rn.f16x2.f32 t, d1, d0;\n\tfma.rn.f16x2 %0, t, %4, %5;\n\t}"
+      : "=r"(out) : "r"(w), "f"(mean), "f"(rstd), "r"(g), "r"(b));
+  return out;
+}
+// (x * rstd) -> fp16 pair, then * g in packed fp16.
+__device__ __forceinline__ uint32_t h2_norm_scale(uint32_t w, float rstd, uint32_t g) {
+  uint32_t out;
+  asm("{\n\t.reg .b16 lo, hi;\n\t.reg .f32 d0, d1;\n\t.reg .b32 t;\n\tmov.b32 {lo, hi}, %1;\n\t"
+      "sub.rn.f32.f16 d0, lo, 0f00000000;\n\tsub.rn.f32.f16 d1, hi, 0f00000000;\n\t"
+      "mul.rn.f32 d0, d0, %2;\n\tmul.rn.f32 d1, d1, %2;\n\t"
+      "cvt.rn.f16x2.f32 t, d1, d0;\n\tmul.rn.f16x2 %0, t, %3;\n\t}"
+      : "=r"(out) : "r"(w), "f"(rstd), "r"(g));
+  return out;
+}
+__device__ __forceinline__ uint32_t &word(uint4 &v, int c) { return c == 0 ? v.x : c == 1 ? v.y : c == 2 ? v.z : v.w; }
+
+static __device__ int g_norm_status = 0;
+
+// Persistent ring kernel (rowring.cuh): one warp per row, the row pulled from the warp's
+// shared-memory ring into registers (packed, VPL 16-byte vectors per lane), gains and biases held in
+// registers for the whole launch.  Rows up to 8 KiB.
+template <typename T, int VPL, bool RMS>
+__global__ void __launch_bounds__(ring::THREADS, 1)
+norm_ring_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict__ w,
+                 const T *__restrict__ b, float *__restrict__ mean_out, float *__restrict__ rstd_out,
+                 int64_t rows, int nvec, int64_t xs, int64_t ys, float inv_n, float eps, int slots,
+                 int slot_bytes, int map, int dbg) {
+  constexpr int E = Vec16<T>::N;
+  using Raw = decltype(Vec16<T>::raw);
+  extern __shared__ uint8_t smem_raw[];
+  ring::WarpRing rg = ring::setup(smem_raw, slots, slot_bytes, (dbg >> 8) & 1);
+  const int store_mode = (dbg >> 4) & 3;
+  dbg &= 15;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t row_bytes = (uint32_t)nvec * 16u;
+  const ring::RowWalk walk = ring::row_walk(rows, map);
+  const int64_t stride_rows = walk.step, first = walk.first, row_end = walk.end;
+  (void)warp;
+
+  if (lane == 0) {
+    for (int s = 0; s < slots; ++s) {
+      const int64_t r = first + (int64_t)s * stride_rows;
+      if (r < row_end) rg.arm(s, x + r * xs, row_bytes);
+    }
+  }
+  // Widest rows: x (64 registers) and the gains (64) stay in registers, the biases live in shared
+  // memory (one 16-byte load per vector and row) so that nothing spills.
+  constexpr bool B_SMEM = false;  // set to (!RMS && VPL == 16) to park the biases in shared memory
+  constexpr int BREG = (RMS || B_SMEM) ? 1 : VPL;
+  Vec16<T> wv[VPL], bv[BREG];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int vi = lane + 32 * j;
+    wv[j].raw = vi < nvec ? __ldg(reinterpret_cast<const Raw *>(w) + vi) : Raw{};
+    if constexpr (!RMS && !B_SMEM) bv[j].raw = vi < nvec ? __ldg(reinterpret_cast<const Raw *>(b) + vi) : Raw{};
+  }
+  if constexpr (B_SMEM) {
+    for (int vi = threadIdx.x; vi < nvec; vi += ring::THREADS)
+      ring::sts128(rg.extra + (uint32_t)vi * 16u, __ldg(reinterpret_cast<const uint4 *>(b) + vi));
+    __syncthreads();
+  }
+
+  int s = 0;
+  uint32_t phase = 0;
+  for (int64_t r = first; r < row_end; r += stride_rows) {
+    if (!tc::mbar_wait(rg.bar(s), phase, rg.abort_flag)) break;
+    Vec16<T> xv[VPL];
+    float sum = 0.f;
+    const uint32_t slot = rg.slot_addr(s);
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int vi = lane + 32 * j;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (vi < nvec) raw = ring::lds128(slot + (uint32_t)vi * 16u);
+      xv[j].raw = *reinterpret_cast<Raw *>(&raw);
+    }
+    if constexpr (sizeof(T) == 2) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        uint4 &raw = *reinterpret_cast<uint4 *>(&xv[j].raw);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if constexpr (RMS) h2_sumsq(word(raw, c), acc[c]);
+          else h2_sum(word(raw, c), acc[c]);
+        }
+      }
+      sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        float f[E];
+        xv[j].unpack(f);
+#pragma unroll
+        for (int e = 0; e < E; ++e) sum += RMS ? f[e] * f[e] : f[e];
+      }
+    }
+    sum = warp_sum(sum);  // every lane's shared loads have completed once this returns
+    if (lane == 0) {
+      const int64_t rn = r + (int64_t)slots * stride_rows;
+      if (rn < row_end) {
+        tc::fence_proxy_async_smem();
+        rg.arm(s, x + rn * xs, row_bytes);
+      }
+    }
+    float mean = 0.f, rstd;
+    if constexpr (RMS) {
+      rstd = 1.0f / sqrtf(sum * inv_n + eps);
+    } else {
+      mean = sum * inv_n;
+      float q = 0.f;
+      if constexpr (sizeof(T) == 2) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          if (lane + 32 * j < nvec) {
+            uint4 &raw = *reinterpret_cast<uint4 *>(&xv[j].raw);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) h2_centred_sumsq(word(raw, c), mean, acc[c]);
+          }
+        }
+        q = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          if (lane + 32 * j < nvec) {
+            float f[E];
+            xv[j].unpack(f);
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+              const float d = f[e] - mean;
+              q = fmaf(d, d, q);
+            }
+          }
+        }
+      }
+      q = warp_sum(q);
+      rstd = 1.0f / sqrtf(q * inv_n + eps);
+      if (lane == 0) {
+        if (mean_out) mean_out[r] = mean;
+        if (rstd_out) rstd_out[r] = rstd;
+      }
+    }
+    T *yr = y + r * ys;
+    if (dbg) {  // measurement aid: 1 = no output stores, 2 = store the row unchanged
+      if (dbg == 2) {
+#pragma unroll
+        for (int j = 0; j < VPL; ++j)
+          if (lane + 32 * j < nvec)
+            ring::store_out16(yr + (int64_t)(lane + 32 * j) * E, *reinterpret_cast<uint4 *>(&xv[j].raw), store_mode, rg.policy);
+      }
+      if (++s == slots) { s = 0; phase ^= 1u; }
+      continue;
+    }
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int vi = lane + 32 * j;
+      if constexpr (sizeof(T) == 2) {
+        if (vi < nvec) {
+          uint4 &xr = *reinterpret_cast<uint4 *>(&xv[j].raw);
+          uint4 &gr = *reinterpret_cast<uint4 *>(&wv[j].raw);
+          uint4 o;
+          if constexpr (RMS) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) word(o, c) = h2_norm_scale(word(xr, c), rstd, word(gr, c));
+          } else {
+            uint4 br;
+            if constexpr (B_SMEM) br = ring::lds128(rg.extra + (uint32_t)vi * 16u);
+            else br = *reinterpret_cast<uint4 *>(&bv[j].raw);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              word(o, c) = h2_norm_affine(word(xr, c), mean, rstd, word(gr, c), word(br, c));
+          }
+          ring::store_out16(yr + (int64_t)vi * E, o, store_mode, rg.policy);
+        }
+      } else if (vi < nvec) {
+        float f[E], wf[E], bf[E];
+        xv[j].unpack(f);
+        wv[j].unpack(wf);
+        if constexpr (B_SMEM) {
+          uint4 raw = ring::lds128(rg.extra + (uint32_t)vi * 16u);
+          Vec16<T> bt;
+          bt.raw = *reinterpret_cast<Raw *>(&raw);
+          bt.unpack(bf);
+        } else if constexpr (!RMS) {
+          bv[j].unpack(bf);
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+          f[e] = RMS ? (f[e] * rstd) * wf[e] : fmaf((f[e] - mean) * rstd, wf[e], bf[e]);
+        Vec16<T> o;
+        o.pack(f);
+        st_stream_as<Raw>(yr + (int64_t)vi * E, o.raw);
+      }
+    }
+    if (++s == slots) { s = 0; phase ^= 1u; }
+  }
+  if (*rg.abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);  // let copies in flight land before the CTA retires
+    if (threadIdx.x == 0) atomicExch(&g_norm_status, (int)HEXB_ERR_TIMEOUT);
+  }
+}
+
+template <typename T, int VPL, bool RMS>
+static int launch_norm_ring(const T *x, T *y, const T *w, const T *b, float *mean, float *rstd,
+                            int64_t rows, int nvec, int64_t xs, int64_t ys, float inv_n, float eps,
+                            int sm_count, cudaStream_t st) {
+  const ring::Layout lay = ring::make_layout(nvec * 16, 0);
+  auto kern = norm_ring_kernel<T, VPL, RMS>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_done[dev & 63]) {
+    HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 212 * 1024));
+    attr_done[dev & 63] = true;
+  }
+  const int64_t groups = (rows + ring::WARPS - 1) / ring::WARPS;
+  const int grid = (int)(groups < sm_count ? groups : sm_count);
+  kern<<<grid, ring::THREADS, lay.smem_bytes, st>>>(x, y, w, b, mean, rstd, rows, nvec, xs, ys, inv_n,
+                                                    eps, lay.slots, lay.slot_bytes, option("ring_map", 0),
+      option("ring_dbg", 0));
+  return check_launch(RMS ? "rms_norm_ring" : "layer_norm_ring");
+}
+
 // Any width / alignment: one CTA per row, the reference's pass structure over global memory
 // (sum; centred squares; normalise).  Rows this path sees are short or odd-sized, so the re-reads
 // are served by L1/L2.
@@ -160,6 +413,21 @@ static int norm_launch(const T *x, T *y, const T *w, const T *b, float *mean, fl
   const float inv_n = 1.0f / (float)cols;
   const bool vec_ok = (cols % E == 0) && (xs % E == 0) && (ys % E == 0) && aligned16(x) &&
                       aligned16(y) && aligned16(w) && (RMS || aligned16(b));
+  const int64_t row_bytes = cols * (int64_t)sizeof(T);
+  if (vec_ok && option("norm_ring", 1) && row_bytes >= 512 && row_bytes <= ring::MAX_ROW_BYTES &&
+      rows * row_bytes >= (4ll << 20)) {
+    const int nvec = (int)(cols / E);
+    const int need = (nvec + 31) / 32;
+#define RING(VPL)                                                                                  \
+  return launch_norm_ring<T, VPL, RMS>(x, y, w, b, mean, rstd, rows, nvec, xs, ys, inv_n, eps,      \
+                                       di.sm_count, st)
+    if (need <= 1) RING(1);
+    if (need <= 2) RING(2);
+    if (need <= 4) RING(4);
+    if (need <= 8) RING(8);
+    RING(16);
+#undef RING
+  }
   int tpr = 0, vpt = 0;
   const int vpt_max = option("norm_vpt_max", sizeof(T) == 2 ? 4 : 8);
   if (vec_ok && !option("norm_force_stream", 0) && choose_row_shape(cols / E, vpt_max, &tpr, &vpt)) {
@@ -181,6 +449,14 @@ static int norm_launch(const T *x, T *y, const T *w, const T *b, float *mean, fl
         x, y, w, b, mean, rstd, rows, cols, xs, ys, inv_n, eps);
   }
   return check_launch(RMS ? "rms_norm" : "layer_norm");
+}
+
+int norm_device_status_fetch_and_clear(int *out) {
+  int v = 0, zero = 0;
+  HEXB_CUDA_OK(cudaMemcpyFromSymbol(&v, g_norm_status, sizeof(int)));
+  if (v) HEXB_CUDA_OK(cudaMemcpyToSymbol(g_norm_status, &zero, sizeof(int)));
+  *out = v;
+  return HEXB_OK;
 }
 
 }  // namespace hexb

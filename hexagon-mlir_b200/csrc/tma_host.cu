@@ -59,6 +59,8 @@ int encode_tmap_f16_sw128(CUtensorMap *out, const void *base, int rank, const ui
 
 int gemm_device_status_fetch_and_clear(int *out);
 int attn_device_status_fetch_and_clear(int *out);
+int norm_device_status_fetch_and_clear(int *out);
+int softmax_device_status_fetch_and_clear(int *out);
 
 }  // namespace hexb
 
@@ -66,9 +68,11 @@ extern "C" int hexb_device_status(int *out) {
   using namespace hexb;
   if (!out) return HEXB_ERR_BAD_ARG;
   HEXB_CUDA_OK(cudaDeviceSynchronize());
-  int a = 0, b = 0;
-  if (int s = gemm_device_status_fetch_and_clear(&a)) return s;
-  if (int s = attn_device_status_fetch_and_clear(&b)) return s;
-  *out = a ? a : b;
+  int v[4] = {0, 0, 0, 0};
+  if (int s = gemm_device_status_fetch_and_clear(&v[0])) return s;
+  if (int s = attn_device_status_fetch_and_clear(&v[1])) return s;
+  if (int s = norm_device_status_fetch_and_clear(&v[2])) return s;
+  if (int s = softmax_device_status_fetch_and_clear(&v[3])) return s;
+  *out = v[0] ? v[0] : v[1] ? v[1] : v[2] ? v[2] : v[3];
   return HEXB_OK;
 }
