@@ -40,18 +40,37 @@ struct Cfg {
   static constexpr int CHUNKS = HD / 64;             // 64-column (128-byte) swizzle chunks
   static constexpr int TILE_BYTES = 128 * HD * 2;    // Q, K or V tile
   static constexpr int CHUNK_BYTES = 128 * 128;      // 128 rows x 128 bytes
-  static constexpr int BAR_BYTES = 8 * 8 + 16;
+  static constexpr int BAR_BYTES = 10 * 8 + 16;
   static constexpr int NEEDED = 3 * TILE_BYTES + BAR_BYTES + 1024;
   static constexpr int SMEM_BYTES = NEEDED < 100 * 1024 ? 100 * 1024 : NEEDED;  // caps residency at 2 CTAs/SM
   static constexpr int TMEM_COLS = 256;              // S: [0,128)  (P aliases [0,64));  O: [128,128+HD)
   static constexpr int O_COL = 128;
 };
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// {lo, hi} -> packed fp16 pair (lo in bits 0..15)
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
 struct Params {
   __half *out;
   int64_t so_z, so_h, so_n;
   int Z, H, N_CTX;
   int num_q_tiles;
+  int tiles_per_cta;   // query tiles one CTA walks (1 or 2)
+  int ctas_per_bh;     // num_q_tiles / tiles_per_cta
   float scale_log2;
   int causal;
   int out_vec_ok;
@@ -71,22 +90,27 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t sQ = smem_addr, sK = sQ + cfg::TILE_BYTES, sV = sK + cfg::TILE_BYTES;
   const uint32_t bar0 = sV + cfg::TILE_BYTES;
   const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = bar0 + 16, v_full = bar0 + 24,
-                 v_empty = bar0 + 32, s_full = bar0 + 40, p_full = bar0 + 48, o_full = bar0 + 56;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 3 * cfg::TILE_BYTES + 64);
+                 v_empty = bar0 + 32, s_full = bar0 + 40, p_full = bar0 + 48, o_full = bar0 + 56,
+                 q_empty = bar0 + 64, o_empty = bar0 + 72;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 3 * cfg::TILE_BYTES + 80);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // work item: heavy (late) query tiles first when causal
-  const int bh_count = p.Z * p.H;
-  const int q_rank = blockIdx.x / bh_count;
-  const int bh = blockIdx.x - q_rank * bh_count;
+  // Work: the CTAs of one (batch, head) are adjacent in launch order, so its K and V stay in L2
+  // while they are re-read.  A CTA walks tiles_per_cta query tiles one after the other; when causal
+  // it pairs a heavy (late) tile with a light (early) one so that every CTA does the same number
+  // of key/value steps, and heavy tiles come first.
+  const int bh = blockIdx.x / p.ctas_per_bh;
+  const int q_rank = blockIdx.x - bh * p.ctas_per_bh;
   const int z = bh / p.H, h = bh - z * p.H;
-  const int q_tile = p.causal ? p.num_q_tiles - 1 - q_rank : q_rank;
-  const int m0 = q_tile * BLOCK_M;
-  int n_kv = (p.N_CTX + BLOCK_N - 1) / BLOCK_N;
-  if (p.causal && q_tile + 1 < n_kv) n_kv = q_tile + 1;
+  const int kv_tiles = (p.N_CTX + BLOCK_N - 1) / BLOCK_N;
+  auto tile_of = [&](int t) {
+    if (p.causal) return t == 0 ? p.num_q_tiles - 1 - q_rank : q_rank;
+    return q_rank * p.tiles_per_cta + t;
+  };
+  auto nkv_of = [&](int q_tile) { return (p.causal && q_tile + 1 < kv_tiles) ? q_tile + 1 : kv_tiles; };
 
   if (threadIdx.x == 0) {
     tc::mbar_init(q_full, 1);
@@ -97,6 +121,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tc::mbar_init(s_full, 1);
     tc::mbar_init(p_full, 4);
     tc::mbar_init(o_full, 1);
+    tc::mbar_init(q_empty, 1);
+    tc::mbar_init(o_empty, 4);
     *abort_flag = 0;
     tc::fence_barrier_init();
     tc::prefetch_tensormap(&tmQ);
@@ -116,22 +142,30 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      tc::mbar_arrive_expect_tx(q_full, cfg::TILE_BYTES);
-#pragma unroll
-      for (int c = 0; c < cfg::CHUNKS; ++c)
-        tc::tma_load_4d(sQ + c * cfg::CHUNK_BYTES, &tmQ, c * 64, m0, h, z, q_full);
-      for (int j = 0; j < n_kv; ++j) {
-        const uint32_t ph = (uint32_t)j & 1u;
-        if (!tc::mbar_wait(k_empty, ph ^ 1u, abort_flag)) break;
-        tc::mbar_arrive_expect_tx(k_full, cfg::TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < cfg::CHUNKS; ++c)
-          tc::tma_load_4d(sK + c * cfg::CHUNK_BYTES, &tmK, c * 64, j * BLOCK_N, h, z, k_full);
-        if (!tc::mbar_wait(v_empty, ph ^ 1u, abort_flag)) break;
-        tc::mbar_arrive_expect_tx(v_full, cfg::TILE_BYTES);
+      uint32_t it = 0;  // key/value steps so far, across tiles
+      bool ok = true;
+      for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
+        const int q_tile = tile_of(t);
+        const int n_kv = nkv_of(q_tile);
+        // the previous tile's last Q.K^T has read Q
+        if (t > 0 && !tc::mbar_wait(q_empty, (uint32_t)(t - 1) & 1u, abort_flag)) break;
+        tc::mbar_arrive_expect_tx(q_full, cfg::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < cfg::CHUNKS; ++c)
-          tc::tma_load_4d(sV + c * cfg::CHUNK_BYTES, &tmV, c * 64, j * BLOCK_N, h, z, v_full);
+          tc::tma_load_4d(sQ + c * cfg::CHUNK_BYTES, &tmQ, c * 64, q_tile * BLOCK_M, h, z, q_full);
+        for (int j = 0; j < n_kv; ++j, ++it) {
+          const uint32_t ph = it & 1u;
+          if (!tc::mbar_wait(k_empty, ph ^ 1u, abort_flag)) { ok = false; break; }
+          tc::mbar_arrive_expect_tx(k_full, cfg::TILE_BYTES);
+#pragma unroll
+          for (int c = 0; c < cfg::CHUNKS; ++c)
+            tc::tma_load_4d(sK + c * cfg::CHUNK_BYTES, &tmK, c * 64, j * BLOCK_N, h, z, k_full);
+          if (!tc::mbar_wait(v_empty, ph ^ 1u, abort_flag)) { ok = false; break; }
+          tc::mbar_arrive_expect_tx(v_full, cfg::TILE_BYTES);
+#pragma unroll
+          for (int c = 0; c < cfg::CHUNKS; ++c)
+            tc::tma_load_4d(sV + c * cfg::CHUNK_BYTES, &tmV, c * 64, j * BLOCK_N, h, z, v_full);
+        }
       }
     }
   } else if (warp == 1) {
@@ -139,115 +173,123 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc_qk = tc::make_idesc_f16_f32(BLOCK_M, BLOCK_N, 0, 0);
       constexpr uint32_t idesc_pv = tc::make_idesc_f16_f32(BLOCK_M, HD, 0, 1);
-      bool ok = tc::mbar_wait(q_full, 0, abort_flag);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const uint32_t ph = (uint32_t)j & 1u;
-        if (!tc::mbar_wait(k_full, ph, abort_flag)) break;
-        tc::tc_fence_after();
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
+        const int n_kv = nkv_of(tile_of(t));
+        if (!tc::mbar_wait(q_full, (uint32_t)t & 1u, abort_flag)) break;
+        for (int j = 0; j < n_kv; ++j, ++it) {
+          const uint32_t ph = it & 1u;
+          if (!tc::mbar_wait(k_full, ph, abort_flag)) { ok = false; break; }
+          tc::tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off = (uint32_t)((k >> 2) * cfg::CHUNK_BYTES + (k & 3) * 32);
-          tc::mma_f16_ss(tS, tc::make_smem_desc_sw128(sQ + off, 16, 1024),
-                         tc::make_smem_desc_sw128(sK + off, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
-        }
-        tc::mma_commit(s_full);
-        tc::mma_commit(k_empty);
-        if (!tc::mbar_wait(p_full, ph, abort_flag)) break;
-        if (!tc::mbar_wait(v_full, ph, abort_flag)) break;
-        tc::tc_fence_after();
+          for (int k = 0; k < HD / 16; ++k) {
+            const uint32_t off = (uint32_t)((k >> 2) * cfg::CHUNK_BYTES + (k & 3) * 32);
+            tc::mma_f16_ss(tS, tc::make_smem_desc_sw128(sQ + off, 16, 1024),
+                           tc::make_smem_desc_sw128(sK + off, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
+          }
+          tc::mma_commit(s_full);
+          tc::mma_commit(k_empty);
+          if (j == n_kv - 1) tc::mma_commit(q_empty);
+          if (!tc::mbar_wait(p_full, ph, abort_flag)) { ok = false; break; }
+          if (!tc::mbar_wait(v_full, ph, abort_flag)) { ok = false; break; }
+          // the first product of a later tile overwrites O: the previous epilogue must have read it
+          if (j == 0 && t > 0 && !tc::mbar_wait(o_empty, (uint32_t)(t - 1) & 1u, abort_flag)) { ok = false; break; }
+          tc::tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < BLOCK_N / 16; ++k) {
-          // A = P rows from TMEM (16 fp16 = 8 columns per step); B = V: 16 kv rows = 2 swizzle atoms.
-          tc::mma_f16_ts(tO, tP + (uint32_t)(k * 8),
-                         tc::make_smem_desc_sw128(sV + (uint32_t)(k * 2048), p.v_lbo, p.v_sbo),
-                         idesc_pv, (j | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < BLOCK_N / 16; ++k) {
+            // A = P rows from TMEM (16 fp16 = 8 columns per step); B = V: 16 kv rows = 2 swizzle atoms.
+            tc::mma_f16_ts(tO, tP + (uint32_t)(k * 8),
+                           tc::make_smem_desc_sw128(sV + (uint32_t)(k * 2048), p.v_lbo, p.v_sbo),
+                           idesc_pv, (j | k) != 0 ? 1u : 0u);
+          }
+          tc::mma_commit(v_empty);
+          if (j == n_kv - 1) tc::mma_commit(o_full);
         }
-        tc::mma_commit(v_empty);
-        if (j == n_kv - 1) tc::mma_commit(o_full);
       }
     }
   } else {
     // ------------------------------------------------------------ softmax / correction / epilogue
     const int q = warp & 3;
     const int r = q * 32 + lane;       // row inside the tile == TMEM lane
-    const int qi = m0 + r;             // query index
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-    float m_ref = -INFINITY, l = 0.f;
+    uint32_t it = 0;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      if (!tc::mbar_wait(s_full, (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
-      tc::tc_fence_after();
-      const int kv0 = j * BLOCK_N;
-      const bool need_mask = (p.causal && kv0 + BLOCK_N - 1 > m0) || (kv0 + BLOCK_N > p.N_CTX);
-      // pass 1: row maximum of the scaled scores
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t v[32];
-        tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c * 32), v);
+    for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
+      const int q_tile = tile_of(t);
+      const int n_kv = nkv_of(q_tile);
+      const int m0 = q_tile * BLOCK_M;
+      const int qi = m0 + r;           // query index
+      float m_ref = -INFINITY, l = 0.f;
+      for (int j = 0; j < n_kv; ++j, ++it) {
+        if (!tc::mbar_wait(s_full, it & 1u, abort_flag)) { ok = false; break; }
+        tc::tc_fence_after();
+        const int kv0 = j * BLOCK_N;
+        const bool need_mask = (p.causal && kv0 + BLOCK_N - 1 > m0) || (kv0 + BLOCK_N > p.N_CTX);
+        // The whole score row (128 fp32) comes into registers with one wait.
+        uint32_t sv[BLOCK_N];
+#pragma unroll
+        for (int c = 0; c < BLOCK_N / 32; ++c)
+          tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c * 32), reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
         tc::tmem_ld_wait();
         if (need_mask) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int kv = kv0 + c * 32 + e;
-            const bool dead = (p.causal && kv > qi) || kv >= p.N_CTX;
-            mx = fmaxf(mx, dead ? -INFINITY : __uint_as_float(v[e]));
+          for (int e = 0; e < BLOCK_N; ++e) {
+            const int kv = kv0 + e;
+            if ((p.causal && kv > qi) || kv >= p.N_CTX) sv[e] = 0xff800000u;  // -inf: exp2 gives 0
           }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
         }
-      }
-      mx *= p.scale_log2;  // scale > 0: max commutes with the scaling
-      const float m_new = fmaxf(m_ref, mx);
-      if (j == 0) {
-        m_ref = m_new;
-      } else if (__any_sync(0xffffffffu, m_new - m_ref > kRescaleThreshold)) {
-        // S_j complete implies P_{j-1}.V_{j-1} complete (MMAs retire in issue order): O is quiescent.
-        const float alpha = exp2f(m_ref - m_new);
-        m_ref = m_new;
-        l *= alpha;
-#pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t o[32];
-          tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(c * 32), o);
-          tc::tmem_ld_wait();
+        // row maximum: three-input max, four independent chains
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-          tc::tmem_st_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+        for (int e = 0; e < BLOCK_N; e += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mx4[u] = max3(mx4[u], __uint_as_float(sv[e + 2 * u]), __uint_as_float(sv[e + 2 * u + 1]));
         }
-      }
-      // pass 2: P = exp2(S*scale - m_ref) as fp16 over the S columns, running row sum
-      const float neg_m = -m_ref;
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        mx *= p.scale_log2;  // scale > 0: max commutes with the scaling
+        const float m_new = fmaxf(m_ref, mx);
+        if (j == 0) {
+          m_ref = m_new;
+        } else if (__any_sync(0xffffffffu, m_new - m_ref > kRescaleThreshold)) {
+          // S_j complete implies P_{j-1}.V_{j-1} complete (MMAs retire in issue order): O is quiescent.
+          const float alpha = ex2_approx(m_ref - m_new);
+          m_ref = m_new;
+          l *= alpha;
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t v[32];
-        tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c * 32), v);
-        tc::tmem_ld_wait();
-        uint32_t pk[16];
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+            tc::tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0 = exp2f(fmaf(__uint_as_float(v[e]), p.scale_log2, neg_m));
-          float p1 = exp2f(fmaf(__uint_as_float(v[e + 1]), p.scale_log2, neg_m));
-          if (need_mask) {
-            const int kv = kv0 + c * 32 + e;
-            if ((p.causal && kv > qi) || kv >= p.N_CTX) p0 = 0.f;
-            if ((p.causal && kv + 1 > qi) || kv + 1 >= p.N_CTX) p1 = 0.f;
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tc::tmem_st_32x32(tO + lane_off + (uint32_t)(c * 32), o);
           }
-          const __half2 hp = __floats2half2_rn(p0, p1);
-          // the sum uses the rounded values the second product will see
-          const float2 back = __half22float2(hp);
-          l += back.x + back.y;
-          pk[e >> 1] = *reinterpret_cast<const uint32_t *>(&hp);
         }
-        tc::tmem_st_32x16(tP + lane_off + (uint32_t)(c * 16), pk);
+        // P = exp2(S*scale - m_ref) as fp16 over the S columns; running row sum in fp32
+        const float neg_m = -m_ref;
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < BLOCK_N / 32; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + e]), p.scale_log2, neg_m));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + e + 1]), p.scale_log2, neg_m));
+            l0 += p0;
+            l1 += p1;
+            pk[e >> 1] = pack_f16x2(p0, p1);
+          }
+          tc::tmem_st_32x16(tP + lane_off + (uint32_t)(c * 16), pk);
+        }
+        l += l0 + l1;
+        tc::tmem_st_wait();
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(p_full);
       }
-      tc::tmem_st_wait();
-      tc::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(p_full);
-    }
-    if (ok && tc::mbar_wait(o_full, 0, abort_flag)) {
+      if (!ok || !tc::mbar_wait(o_full, (uint32_t)t & 1u, abort_flag)) { ok = false; break; }
       tc::tc_fence_after();
       const float inv = 1.0f / l;
       __half *orow = p.out + (int64_t)z * p.so_z + (int64_t)h * p.so_h + (int64_t)qi * p.so_n;
@@ -256,6 +298,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         uint32_t o[32];
         tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(c * 32), o);
         tc::tmem_ld_wait();
+        if (c == HD / 32 - 1) {  // O is in registers: the next tile's first product may overwrite it
+          tc::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(o_empty);
+        }
         if (qi < p.N_CTX) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
@@ -405,7 +452,10 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, __half *
   p.out_vec_ok = aligned16(O) && s[9] % 8 == 0 && s[10] % 8 == 0 && s[11] % 8 == 0;
   p.v_lbo = (uint32_t)option("attn_v_lbo", cfg::CHUNK_BYTES);
   p.v_sbo = (uint32_t)option("attn_v_sbo", 1024);
-  const int64_t ctas = (int64_t)p.num_q_tiles * Z * H;
+  // pairing pays when the tiles differ in length (causal); equal tiles run slightly faster one per CTA
+  p.tiles_per_cta = (p.num_q_tiles % 2 == 0 && option("attn_tiles_per_cta", causal ? 2 : 1) == 2) ? 2 : 1;
+  p.ctas_per_bh = p.num_q_tiles / p.tiles_per_cta;
+  const int64_t ctas = (int64_t)p.ctas_per_bh * Z * H;
   if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
   kern<<<(unsigned)ctas, THREADS, cfg::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2], p);
   return check_launch("attn_tc");
