@@ -454,6 +454,16 @@ def e2e_generic(wl, steps):
 
 # ---------------------------------------------------------------------------- main
 def main():
+    # stdout must carry exactly one JSON line: keep a private handle to it and point fd 1 at stderr,
+    # so that anything a library prints (NCCL's version banner, warnings) cannot land beside it.
+    sys.stdout.flush()
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+    def emit(obj):
+        real_stdout.write(json.dumps(obj) + "\n")
+        real_stdout.flush()
+
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -487,7 +497,7 @@ def main():
                                  "sample": sample},
                 "e2e": {"value": round(val / scale, 4), "unit": wl_cls.unit, "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        emit(line)
         return 0
 
     if not torch.cuda.is_available():
@@ -578,7 +588,7 @@ def main():
         line["cpu_baseline"] = None
 
     if rank == 0:
-        print(json.dumps(line))
+        emit(line)
     if dist:
         dist.barrier()
         dist.destroy_process_group()

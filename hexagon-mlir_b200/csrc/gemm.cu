@@ -101,7 +101,8 @@ template <int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
-               int64_t ldr, int tiles_m, int tiles_n, int vec_ok, uint32_t b_lbo, uint32_t b_sbo) {
+               int64_t ldr, int tiles_m, int tiles_n, int vec_ok, uint32_t b_lbo, uint32_t b_sbo,
+               int full_items, int split) {
   using cfg = Cfg<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
@@ -144,8 +145,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Work items.  Items [0, full_items) are whole 128 x BN tiles; each remaining tile -- the ones of
+  // the last, partial wave over the SMs -- is cut into `split` column slices of BN/split, so that
+  // wave finishes in 1/split of a tile time instead of leaving most SMs idle for a whole one.
   const int num_tiles = tiles_m * tiles_n;
+  const int num_items = full_items + (num_tiles - full_items) * split;
   const int num_kb = (K + BK - 1) / BK;
+  struct Item { int tm, col0, width; };
+  auto item_of = [&](int i) {
+    Item it;
+    int tile = i, sub = 0;
+    it.width = BN;
+    if (i >= full_items) {
+      const int k = i - full_items;
+      tile = full_items + k / split;
+      sub = k - (k / split) * split;
+      it.width = BN / split;
+    }
+    it.tm = tile % tiles_m;
+    it.col0 = (tile / tiles_m) * BN + sub * it.width;
+    return it;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -153,17 +173,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int tm = tile % tiles_m, tn = tile / tiles_m;
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const Item w = item_of(item);
+        const int chunks = w.width / 64;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!tc::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t sa = smem_addr + stage * cfg::STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
-          tc::mbar_arrive_expect_tx(full_bar(stage), cfg::STAGE_BYTES);
-          tc::tma_load_2d(sa, &tmA, kb * BK, tm * BM, full_bar(stage));
+          tc::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(A_BYTES + chunks * BK * 128));
+          tc::tma_load_2d(sa, &tmA, kb * BK, w.tm * BM, full_bar(stage));
 #pragma unroll
           for (int j = 0; j < BN / 64; ++j)
-            tc::tma_load_2d(sb + j * (BK * 128), &tmB, tn * BN + j * 64, kb * BK, full_bar(stage));
+            if (j < chunks) tc::tma_load_2d(sb + j * (BK * 128), &tmB, w.col0 + j * 64, kb * BK, full_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -171,12 +192,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = tc::make_idesc_f16_f32(BM, BN, 0, 1);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int t = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++t) {
+        const uint32_t idesc = tc::make_idesc_f16_f32(BM, item_of(item).width, 0, 1);
         const int acc = t & 1;
         if (!tc::mbar_wait(tempty_bar(acc), ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag)) break;
         tc::tc_fence_after();
@@ -204,8 +225,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     int t = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
-      const int tm = tile % tiles_m, tn = tile / tiles_m;
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x, ++t) {
+      const Item w = item_of(item);
+      const int tm = w.tm;
       const int acc = t & 1;
       if (!tc::mbar_wait(tfull_bar(acc), (uint32_t)(t >> 1) & 1u, abort_flag)) break;
       tc::tc_fence_after();
@@ -214,11 +236,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       OutT *crow = C + (int64_t)row * ldc;
       const __half *rrow = R ? R + (int64_t)row * ldr : nullptr;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < w.width / 32; ++c) {
         uint32_t v[32];
         tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
         tc::tmem_ld_wait();
-        const int col0 = tn * BN + c * 32;
+        const int col0 = w.col0 + c * 32;
         if (row < M && col0 < N) store_row_chunk<OutT>(crow, rrow, v, col0, N, vec_ok != 0);
       }
       tc::tc_fence_before();
@@ -280,11 +302,19 @@ static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, co
   }
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const int tiles = tiles_m * tiles_n;
-  const int grid = tiles < sm_count ? tiles : sm_count;
+  // split the tiles of the last partial wave into column slices (>= 64 wide) while they still fit one wave
+  int full_items = tiles / sm_count * sm_count, split = 1;
+  const int rem = tiles - full_items;
+  if (rem > 0 && option("gemm_tail_split", 1)) {
+    while (split * 2 <= BN / 64 && rem * split * 2 <= sm_count) split *= 2;
+  }
+  if (split == 1) full_items = tiles;
+  const int items = full_items + (tiles - full_items) * split;
+  const int grid = items < sm_count ? items : sm_count;
   const uint32_t lbo = (uint32_t)option("gemm_b_lbo", BK * 128);
   const uint32_t sbo = (uint32_t)option("gemm_b_sbo", 1024);
   kern<<<grid, THREADS, cfg::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n,
-                                               vec_ok, lbo, sbo);
+                                               vec_ok, lbo, sbo, full_items, split);
   return check_launch("gemm_tc");
 }
 
