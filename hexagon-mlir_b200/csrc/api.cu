@@ -80,8 +80,9 @@ int current_device(DeviceInfo *out) {
 struct Staging {
   void *ptr = nullptr;
   size_t bytes = 0;
+  static constexpr int kMaxChunks = 64;
   cudaStream_t streams[3] = {nullptr, nullptr, nullptr};
-  cudaEvent_t events[8] = {};
+  cudaEvent_t ev_in[kMaxChunks] = {}, ev_k[kMaxChunks] = {};
   bool ready = false;
 };
 static Staging g_staging[64];
@@ -94,7 +95,8 @@ static int staging_get(size_t bytes, Staging **out) {
   Staging &s = g_staging[dev];
   if (!s.ready) {
     for (auto &st : s.streams) HEXB_CUDA_OK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
-    for (auto &ev : s.events) HEXB_CUDA_OK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    for (auto &ev : s.ev_in) HEXB_CUDA_OK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    for (auto &ev : s.ev_k) HEXB_CUDA_OK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
     s.ready = true;
   }
   if (s.bytes < bytes) {
@@ -111,9 +113,12 @@ static int staging_get(size_t bytes, Staging **out) {
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static inline size_t dt_size(int dt) { return dt == HEXB_DT_F16 ? 2 : dt == HEXB_DT_F32 ? 4 : 0; }
 
-// Row-wise operators: the rows are cut into chunks that run as H2D copy -> kernel -> D2H copy on
-// rotating streams, so that the upload of chunk i+1, the kernel of chunk i and the download of
-// chunk i-1 overlap (PCIe is full duplex).  `launch(x_dev, y_dev, row0, nrows, stream)`.
+// Row-wise operators: the rows are cut into chunks that flow through three streams -- upload,
+// compute, download -- chained by events, so that the upload of chunk i+1, the kernel of chunk i
+// and the download of chunk i-1 overlap (PCIe is full duplex and each direction has its own copy
+// engine).  `launch(x_dev, y_dev, extra_dev, row0, nrows, stream)`; a call with x_dev == nullptr
+// uploads the operator's small operands (gains, biases), one with nrows == -1 downloads its small
+// results (statistics) after the last chunk.
 template <typename F>
 static int rows_pipeline(const void *x, void *y, int64_t rows, int64_t cols, size_t esz,
                          size_t extra_bytes, F &&launch_with_extra) {
@@ -128,25 +133,29 @@ static int rows_pipeline(const void *x, void *y, int64_t rows, int64_t cols, siz
   char *dx = (char *)s->ptr, *dy = dx + mat, *de = dy + mat;
   int chunks = option("host_chunks", 8);
   if (chunks < 1) chunks = 1;
+  if (chunks > Staging::kMaxChunks) chunks = Staging::kMaxChunks;
   if ((int64_t)chunks > rows) chunks = (int)rows;
   if ((size_t)rows * row_bytes < ((size_t)4 << 20)) chunks = 1;
-  if (int st = launch_with_extra(nullptr, nullptr, de, 0, 0, s->streams[0])) return st;  // uploads extras
-  HEXB_CUDA_OK(cudaEventRecord(s->events[0], s->streams[0]));
-  for (int i = 1; i < 3; ++i) HEXB_CUDA_OK(cudaStreamWaitEvent(s->streams[i], s->events[0], 0));
+  cudaStream_t s_in = s->streams[0], s_k = s->streams[1], s_out = s->streams[2];
+  if (int st = launch_with_extra(nullptr, nullptr, de, 0, 0, s_in)) return st;  // small operands
   const int64_t per = (rows + chunks - 1) / chunks;
   for (int c = 0; c < chunks; ++c) {
     const int64_t r0 = (int64_t)c * per;
     const int64_t nr = rows - r0 < per ? rows - r0 : per;
     if (nr <= 0) break;
-    cudaStream_t st = s->streams[c % 3];
     const size_t off = (size_t)r0 * row_bytes;
     HEXB_CUDA_OK(cudaMemcpyAsync(dx + off, (const char *)x + off, (size_t)nr * row_bytes,
-                                 cudaMemcpyHostToDevice, st));
-    if (int e = launch_with_extra(dx + off, dy + off, de, r0, nr, st)) return e;
+                                 cudaMemcpyHostToDevice, s_in));
+    HEXB_CUDA_OK(cudaEventRecord(s->ev_in[c], s_in));
+    HEXB_CUDA_OK(cudaStreamWaitEvent(s_k, s->ev_in[c], 0));
+    if (int e = launch_with_extra(dx + off, dy + off, de, r0, nr, s_k)) return e;
+    HEXB_CUDA_OK(cudaEventRecord(s->ev_k[c], s_k));
+    HEXB_CUDA_OK(cudaStreamWaitEvent(s_out, s->ev_k[c], 0));
     HEXB_CUDA_OK(cudaMemcpyAsync((char *)y + off, dy + off, (size_t)nr * row_bytes,
-                                 cudaMemcpyDeviceToHost, st));
+                                 cudaMemcpyDeviceToHost, s_out));
   }
-  for (auto &st : s->streams) HEXB_CUDA_OK(cudaStreamSynchronize(st));
+  if (int st = launch_with_extra(dx, dy, de, 0, -1, s_out)) return st;  // small results
+  HEXB_CUDA_OK(cudaStreamSynchronize(s_out));
   return HEXB_OK;
 }
 
@@ -210,7 +219,7 @@ extern "C" int hexb_softmax_host(int dtype, const void *x, void *y, int64_t rows
   std::lock_guard<std::mutex> lk(g_staging_mu);
   return rows_pipeline(x, y, rows, cols, esz, 0,
                        [&](void *dx, void *dy, void *, int64_t, int64_t nr, cudaStream_t st) -> int {
-                         if (!dx) return HEXB_OK;
+                         if (!dx || nr < 0) return HEXB_OK;
                          return dtype == HEXB_DT_F16
                                     ? hexb_softmax_f16(dx, dy, nr, cols, cols, cols, st)
                                     : hexb_softmax_f32((const float *)dx, (float *)dy, nr, cols, cols, cols, st);
@@ -235,14 +244,15 @@ extern "C" int hexb_layer_norm_host(int dtype, const void *x, void *y, const voi
           HEXB_CUDA_OK(cudaMemcpyAsync(db, b, (size_t)cols * esz, cudaMemcpyHostToDevice, s));
           return HEXB_OK;
         }
-        int e = dtype == HEXB_DT_F16
-                    ? hexb_layer_norm_f16(dx, dy, dw, db, dm + r0, dr + r0, nr, cols, cols, cols, eps, s)
-                    : hexb_layer_norm_f32((const float *)dx, (float *)dy, (const float *)dw,
-                                          (const float *)db, dm + r0, dr + r0, nr, cols, cols, cols, eps, s);
-        if (e) return e;
-        if (mean) HEXB_CUDA_OK(cudaMemcpyAsync(mean + r0, dm + r0, (size_t)nr * 4, cudaMemcpyDeviceToHost, s));
-        if (rstd) HEXB_CUDA_OK(cudaMemcpyAsync(rstd + r0, dr + r0, (size_t)nr * 4, cudaMemcpyDeviceToHost, s));
-        return HEXB_OK;
+        if (nr < 0) {  // statistics of all rows, after the last chunk
+          if (mean) HEXB_CUDA_OK(cudaMemcpyAsync(mean, dm, (size_t)rows * 4, cudaMemcpyDeviceToHost, s));
+          if (rstd) HEXB_CUDA_OK(cudaMemcpyAsync(rstd, dr, (size_t)rows * 4, cudaMemcpyDeviceToHost, s));
+          return HEXB_OK;
+        }
+        return dtype == HEXB_DT_F16
+                   ? hexb_layer_norm_f16(dx, dy, dw, db, dm + r0, dr + r0, nr, cols, cols, cols, eps, s)
+                   : hexb_layer_norm_f32((const float *)dx, (float *)dy, (const float *)dw,
+                                         (const float *)db, dm + r0, dr + r0, nr, cols, cols, cols, eps, s);
       });
   return st;
 }
@@ -261,6 +271,7 @@ extern "C" int hexb_rms_norm_host(int dtype, const void *x, void *y, const void 
           HEXB_CUDA_OK(cudaMemcpyAsync(de, w, (size_t)cols * esz, cudaMemcpyHostToDevice, s));
           return HEXB_OK;
         }
+        if (nr < 0) return HEXB_OK;
         return dtype == HEXB_DT_F16
                    ? hexb_rms_norm_f16(dx, dy, de, nr, cols, cols, cols, eps, s)
                    : hexb_rms_norm_f32((const float *)dx, (float *)dy, (const float *)de, nr, cols, cols, cols, eps, s);
