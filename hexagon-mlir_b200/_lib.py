@@ -58,6 +58,10 @@ PROTOTYPES = {
     "hexb_silu_f32": (_i, [_vp, _vp, _i64, _vp]),
     "hexb_silu_f16": (_i, [_vp, _vp, _i64, _vp]),
     "hexb_swiglu_f16": (_i, [_vp, _vp, _i64, _i64, _vp]),
+    "hexb_unary": (_i, [_i, _i, _vp, _vp, _i64, _vp]),
+    "hexb_binary": (_i, [_i, _i, _vp, _vp, _vp, _i64, _vp]),
+    "hexb_sum": (_i, [_i, _vp, _vp, _i64, _vp]),
+    "hexb_rope": (_i, [_i, _vp, _vp, _i64, _i64, _i64, _i64, C.POINTER(_i64), C.POINTER(_i64), _f, _vp]),
     "hexb_decoder_workspace_bytes": (C.c_size_t, [C.POINTER(DecoderConfig)]),
     "hexb_decoder_forward_f16": (_i, [C.POINTER(DecoderConfig), C.POINTER(DecoderWeights), _vp, _vp, _vp, C.c_size_t, _vp]),
     "hexb_decoder_forward_f16_noalloc": (_i, [C.POINTER(DecoderConfig), C.POINTER(DecoderWeights), _vp, _vp, _vp]),

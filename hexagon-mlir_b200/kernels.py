@@ -78,6 +78,84 @@ def _silu_kernel(x_ptr, output_ptr, BLOCK_SIZE=None):
     ops.silu(x_ptr, output_ptr)
 
 
+def _flat(t, n):
+    if not t.is_contiguous() or t.numel() < n:
+        raise ValueError("tensor does not hold the elements the launch covers")
+    return t.view(-1)[:n]
+
+
+def _covered(x, BLOCK_SIZE, _grid):
+    """Elements one launch touches: programs * BLOCK_SIZE, as the reference kernels index them."""
+    progs = 1
+    for g in (_grid if isinstance(_grid, (tuple, list)) else (_grid,)):
+        progs *= int(g)
+    return min(x.numel(), progs * int(BLOCK_SIZE))
+
+
+def _gelu_kernel(x_ptr, output_ptr, BLOCK_SIZE, _grid=(1,)):
+    n = _covered(x_ptr, BLOCK_SIZE, _grid)
+    ops.unary("gelu_tanh", _flat(x_ptr, n), _flat(output_ptr, n))
+
+
+def _cos_kernel(x_ptr, output_ptr, BLOCK_SIZE, _grid=(1,)):
+    n = _covered(x_ptr, BLOCK_SIZE, _grid)
+    ops.unary("cos", _flat(x_ptr, n), _flat(output_ptr, n))
+
+
+def _sin_kernel(x_ptr, output_ptr, BLOCK_SIZE, _grid=(1,)):
+    n = _covered(x_ptr, BLOCK_SIZE, _grid)
+    ops.unary("sin", _flat(x_ptr, n), _flat(output_ptr, n))
+
+
+def _rsqrt_kernel(x_ptr, output_ptr, BLOCK_SIZE, _grid=(1,)):
+    n = _covered(x_ptr, BLOCK_SIZE, _grid)
+    ops.unary("rsqrt", _flat(x_ptr, n), _flat(output_ptr, n))
+
+
+def _add_kernel(x_ptr, y_ptr, output_ptr, BLOCK_SIZE, _grid=(1,)):
+    n = _covered(x_ptr, BLOCK_SIZE, _grid)
+    ops.binary("add", _flat(x_ptr, n), _flat(y_ptr, n), _flat(output_ptr, n))
+
+
+def _add_kernel_scalar(x_ptr, y_ptr, output_ptr, n_elements, BLOCK_SIZE, _grid=(1,)):
+    n = min(int(n_elements), _covered(x_ptr, BLOCK_SIZE, _grid))
+    ops.binary("add", _flat(x_ptr, n), _flat(y_ptr, n), _flat(output_ptr, n))
+
+
+def _add_2d_kernel(x_ptr, y_ptr, output_ptr, NUM_ROWS, NUM_COLS):
+    n = NUM_ROWS * NUM_COLS
+    ops.binary("add", _flat(x_ptr, n), _flat(y_ptr, n), _flat(output_ptr, n))
+
+
+def _div_kernel(x_ptr, y_ptr, output_ptr, NUM_ROWS, NUM_COLS):
+    n = NUM_ROWS * NUM_COLS
+    ops.binary("div", _flat(x_ptr, n), _flat(y_ptr, n), _flat(output_ptr, n))
+
+
+def _sum_kernel(x_ptr, output_ptr, BLOCK_SIZE, _grid=(1,)):
+    """Program pid writes the sum of its BLOCK_SIZE elements to output[pid] (test_sum.py:31-36)."""
+    progs = int(_grid[0]) if isinstance(_grid, (tuple, list)) else int(_grid)
+    flat = x_ptr.view(-1)
+    for pid in range(progs):
+        ops.vec_sum(flat[pid * BLOCK_SIZE:(pid + 1) * BLOCK_SIZE], output_ptr.view(-1)[pid:pid + 1])
+
+
+def _rope_kernel(x_ptr, output_ptr, BATCH_SIZE, BATCH_SIZE_STRIDE, SEQ_LEN, SEQ_LEN_STRIDE, N_HEADS, N_HEADS_STRIDE,
+                 N_FEATURES, N_FEATURES_STRIDE, BLOCK_SIZE=None, THETA=10000.0):
+    if N_FEATURES_STRIDE != 1:
+        raise ValueError("rope_kernel: N_FEATURES_STRIDE must be 1")
+    shape = (BATCH_SIZE, SEQ_LEN, N_HEADS, N_FEATURES)
+    strides = (BATCH_SIZE_STRIDE, SEQ_LEN_STRIDE, N_HEADS_STRIDE, 1)
+    xv = torch.as_strided(x_ptr, shape, strides, x_ptr.storage_offset())
+    ov = torch.as_strided(output_ptr, shape, strides, output_ptr.storage_offset())
+    if x_ptr.device.type != "cuda":
+        tmp = torch.empty(shape, dtype=x_ptr.dtype)
+        ops.rope(xv.contiguous(), tmp, theta=THETA)
+        ov.copy_(tmp)
+    else:
+        ops.rope(xv, ov, theta=THETA)
+
+
 class KernelLauncher:
     """``launcher[grid](*args, **kwargs)``: binds arguments by the reference kernel's parameter names."""
 
@@ -91,6 +169,8 @@ class KernelLauncher:
     def __getitem__(self, grid):
         def run(*args, **kwargs):
             kargs, _opts = split_options(kwargs, self._params)
+            if "_grid" in self._params:
+                kargs["_grid"] = grid
             bound = self._sig.bind(*args, **kargs)
             self._impl(*bound.args, **bound.kwargs)
             return None
@@ -107,6 +187,16 @@ _REGISTRY = {
     "matmul_hexkl": _matmul,
     "attention_fwd_kernel": _attention_fwd_kernel,
     "silu_kernel": _silu_kernel,
+    "gelu_kernel": _gelu_kernel,
+    "cos_kernel": _cos_kernel,
+    "sin_kernel": _sin_kernel,
+    "rsqrt_kernel": _rsqrt_kernel,
+    "add_kernel": _add_kernel,
+    "add_kernel_scalar": _add_kernel_scalar,
+    "add_2d_kernel": _add_2d_kernel,
+    "div_kernel": _div_kernel,
+    "sum_kernel": _sum_kernel,
+    "rope_kernel": _rope_kernel,
 }
 
 _DTYPE_SUFFIXES = ("_float16", "_float32", "_float64", "_int8", "_int16", "_int32", "_int64", "_uint8",
@@ -134,3 +224,13 @@ matmul = KernelLauncher("matmul", _matmul)
 matmul_hexkl = KernelLauncher("matmul_hexkl", _matmul)
 attention_fwd_kernel = KernelLauncher("attention_fwd_kernel", _attention_fwd_kernel)
 silu_kernel = KernelLauncher("silu_kernel", _silu_kernel)
+gelu_kernel = KernelLauncher("gelu_kernel", _gelu_kernel)
+cos_kernel = KernelLauncher("cos_kernel", _cos_kernel)
+sin_kernel = KernelLauncher("sin_kernel", _sin_kernel)
+rsqrt_kernel = KernelLauncher("rsqrt_kernel", _rsqrt_kernel)
+add_kernel = KernelLauncher("add_kernel", _add_kernel)
+add_kernel_scalar = KernelLauncher("add_kernel_scalar", _add_kernel_scalar)
+add_2d_kernel = KernelLauncher("add_2d_kernel", _add_2d_kernel)
+div_kernel = KernelLauncher("div_kernel", _div_kernel)
+sum_kernel = KernelLauncher("sum_kernel", _sum_kernel)
+rope_kernel = KernelLauncher("rope_kernel", _rope_kernel)

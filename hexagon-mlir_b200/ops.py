@@ -230,6 +230,81 @@ def swiglu(gate_up, out) -> None:
         check(lib.hexb_swiglu_f16(_ptr(gate_up), _ptr(out), rows, cols2 // 2, _stream(gate_up)), "swiglu")
 
 
+UNARY_OPS = {"gelu_tanh": 1, "cos": 2, "sin": 3, "rsqrt": 4}
+BINARY_OPS = {"add": 1, "sub": 2, "mul": 3, "div": 4}
+
+
+def _on_device(*ts):
+    """CUDA tensors pass through; CPU tensors are staged (torch moves the bytes, nothing else)."""
+    host = ts[0].device.type != "cuda"
+    return host, [t.cuda() if host else t for t in ts]
+
+
+def unary(op: str, x, out) -> None:
+    """out = op(x), op in gelu_tanh / cos / sin / rsqrt (reference: test_gelu.py:25-54,
+    test_math_ops.py:24-37, test_rsqrt.py:19-24)."""
+    lib = _lib.load()
+    _same_place(x, out)
+    if x.shape != out.shape or x.dtype != out.dtype or not (x.is_contiguous() and out.is_contiguous()):
+        raise ValueError("unary: x and out must be contiguous with equal shape and dtype")
+    host, (xd,) = _on_device(x)
+    od = torch.empty_like(xd) if host else out
+    with torch.cuda.device(xd.device):
+        check(lib.hexb_unary(UNARY_OPS[op], _dt(x), _ptr(xd), _ptr(od), x.numel(), _stream(xd)), op)
+    if host:
+        out.copy_(od)
+
+
+def binary(op: str, a, b, out) -> None:
+    """out = a op b, op in add / sub / mul / div (reference: test_vec_add.py:19-25,
+    test_vec_add_2d.py:21-56, test_vec_div_2d.py:20-55)."""
+    lib = _lib.load()
+    _same_place(a, b, out)
+    if not (a.shape == b.shape == out.shape) or not (a.dtype == b.dtype == out.dtype):
+        raise ValueError("binary: a, b and out must agree in shape and dtype")
+    if not (a.is_contiguous() and b.is_contiguous() and out.is_contiguous()):
+        raise ValueError("binary: tensors must be contiguous")
+    host, (ad, bd) = _on_device(a, b)
+    od = torch.empty_like(ad) if host else out
+    with torch.cuda.device(ad.device):
+        check(lib.hexb_binary(BINARY_OPS[op], _dt(a), _ptr(ad), _ptr(bd), _ptr(od), a.numel(), _stream(ad)), op)
+    if host:
+        out.copy_(od)
+
+
+def vec_sum(x, out) -> None:
+    """out[0] = sum(x) with fp32 accumulation in a fixed order (reference: test_sum.py:31-36)."""
+    lib = _lib.load()
+    _same_place(x, out)
+    if x.dtype != out.dtype or out.numel() < 1 or not x.is_contiguous():
+        raise ValueError("sum: out must hold one element of x's dtype, x contiguous")
+    host, (xd,) = _on_device(x)
+    od = torch.empty(1, dtype=x.dtype, device=xd.device) if host else out
+    with torch.cuda.device(xd.device):
+        check(lib.hexb_sum(_dt(x), _ptr(xd), _ptr(od), x.numel(), _stream(xd)), "sum")
+    if host:
+        out.view(-1)[:1].copy_(od)
+
+
+def rope(x, out, theta: float = 10000.0) -> None:
+    """Interleaved-pair rotary embedding of a [B, L, H, D] tensor (reference: test_rope.py:98-190)."""
+    lib = _lib.load()
+    _same_place(x, out)
+    if x.dim() != 4 or x.shape != out.shape or x.dtype != out.dtype:
+        raise ValueError("rope: expected [B, L, H, D] tensors of equal shape and dtype")
+    host, (xd,) = _on_device(x)
+    od = torch.empty_like(xd) if host else out
+    if xd.stride(3) != 1 or od.stride(3) != 1:
+        raise ValueError("rope: innermost stride must be 1")
+    B, L, H, D = x.shape
+    xs = (C.c_int64 * 3)(xd.stride(0), xd.stride(1), xd.stride(2))
+    os_ = (C.c_int64 * 3)(od.stride(0), od.stride(1), od.stride(2))
+    with torch.cuda.device(xd.device):
+        check(lib.hexb_rope(_dt(x), _ptr(xd), _ptr(od), B, L, H, D, xs, os_, float(theta), _stream(xd)), "rope")
+    if host:
+        out.copy_(od)
+
+
 class DecoderStack:
     """The decoder-only block stack on one GPU: holds the weight pointer tables and the workspace.
 

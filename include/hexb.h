@@ -118,6 +118,25 @@ int hexb_silu_f32(const float *x, float *y, int64_t n, void *stream);
 int hexb_silu_f16(const void *x, void *y, int64_t n, void *stream);
 int hexb_swiglu_f16(const void *gate_up, void *out, int64_t rows, int64_t cols, void *stream);
 
+/* ---- elementwise operators of the remaining Triton tests (dtype = HEXB_DT_F16 / HEXB_DT_F32;
+ * contiguous vectors of n elements; fp32 arithmetic, one rounding).
+ * hexb_unary replaces: gelu_kernel (test/python/triton/test_gelu.py:25-54, tanh form),
+ * cos_kernel / sin_kernel (test_math_ops.py:24-37), rsqrt_kernel (test_rsqrt.py:19-24).
+ * hexb_binary replaces: add_kernel (test_vec_add.py:19-25), add_kernel_scalar
+ * (test_vec_add_with_scalar.py:31-46), add_2d_kernel (test_vec_add_2d.py:21-56), div_kernel
+ * (test_vec_div_2d.py:20-55).
+ * hexb_sum replaces: sum_kernel (test_sum.py:31-36): out[0] = sum(x), fp32 accumulation.
+ * hexb_rope replaces: rope_kernel (test_rope.py:98-190): interleaved-pair rotary embedding of a
+ * [B, L, H, D] tensor (unit innermost stride; strides[0..2] = batch, position, head in elements),
+ * angle = position * theta^(-(d - d%2)/D). */
+enum { HEXB_OP_GELU_TANH = 1, HEXB_OP_COS = 2, HEXB_OP_SIN = 3, HEXB_OP_RSQRT = 4 };
+enum { HEXB_OP_ADD = 1, HEXB_OP_SUB = 2, HEXB_OP_MUL = 3, HEXB_OP_DIV = 4 };
+int hexb_unary(int op, int dtype, const void *x, void *y, int64_t n, void *stream);
+int hexb_binary(int op, int dtype, const void *a, const void *b, void *y, int64_t n, void *stream);
+int hexb_sum(int dtype, const void *x, void *out, int64_t n, void *stream);
+int hexb_rope(int dtype, const void *x, void *out, int64_t B, int64_t L, int64_t H, int64_t D,
+              const int64_t *x_strides, const int64_t *out_strides, float theta, void *stream);
+
 /* ---- decoder-only block stack, forward.  Pre-norm blocks:
  *   h = x + Wo . Attn(RMSNorm(x) . Wqkv);  x' = h + Wd . (SiLU(Wg . n) * (Wu . n)), n = RMSNorm(h)
  * causal attention, no bias, fp16 storage, fp32 accumulation and statistics.

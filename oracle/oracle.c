@@ -313,6 +313,72 @@ void oracle_silu_f16(const f16 *x, f16 *y, int64_t n) {
   }
 }
 
+/* ------------------------------------------------------------------ GELU (tanh form)
+ * gelu_kernel + tanh, test/python/triton/test_gelu.py:25-54:
+ *   tanh(u) = (1 - e) / (1 + e), e = exp((-2u).to(f32)).to(x.dtype);
+ *   y = 0.5 * x * (1 + tanh(0.797885*x + 0.035677*x*x*x)); for fp16 data every step rounds to fp16. */
+void oracle_gelu_f32(const float *x, float *y, int64_t n) {
+#pragma omp parallel for
+  for (int64_t i = 0; i < n; ++i) {
+    const float u = 0.797885f * x[i] + 0.035677f * x[i] * x[i] * x[i];
+    const float e = expf(-2.0f * u);
+    y[i] = 0.5f * x[i] * (1.0f + (1.0f - e) / (1.0f + e));
+  }
+}
+void oracle_gelu_f16(const f16 *x, f16 *y, int64_t n) {
+#pragma omp parallel for
+  for (int64_t i = 0; i < n; ++i) {
+    const f16 xv = x[i];
+    const f16 x3 = (f16)((f16)((f16)((f16)0.035677f * xv) * xv) * xv);
+    const f16 u = (f16)((f16)((f16)0.797885f * xv) + x3);
+    const f16 e = (f16)expf((float)(f16)((f16)-2.0f * u));
+    const f16 th = (f16)((f16)((f16)1.0f - e) / (f16)((f16)1.0f + e));
+    y[i] = (f16)((f16)((f16)0.5f * xv) * (f16)((f16)1.0f + th));
+  }
+}
+
+/* ------------------------------------------------------------------ RoPE
+ * rope_kernel + compute_thetas, test/python/triton/test_rope.py:40-190: steps = [0,0,2,2,...],
+ * freq = 1 / theta^(steps/D), angle = position * freq; even d: x[d]*cos - x[d+1]*sin,
+ * odd d: x[d-1]*sin + x[d]*cos.  Contiguous [B, L, H, D], fp32 arithmetic. */
+void oracle_rope_f32(const float *x, float *y, int64_t B, int64_t L, int64_t H, int64_t D, float theta) {
+#pragma omp parallel for collapse(2)
+  for (int64_t b = 0; b < B; ++b)
+    for (int64_t l = 0; l < L; ++l)
+      for (int64_t h = 0; h < H; ++h) {
+        const int64_t off = ((b * L + l) * H + h) * D;
+        for (int64_t d = 0; d < D; ++d) {
+          const float step = (float)(d - (d % 2));
+          const float freq = 1.0f / expf(logf(theta) * (step / (float)D));
+          const float cs = cosf((float)l * freq), sn = sinf((float)l * freq);
+          y[off + d] = (d % 2 == 0) ? x[off + d] * cs - x[off + d + 1] * sn : x[off + d - 1] * sn + x[off + d] * cs;
+        }
+      }
+}
+void oracle_rope_f16(const f16 *x, f16 *y, int64_t B, int64_t L, int64_t H, int64_t D, float theta) {
+  const int64_t n = B * L * H * D;
+  float *xf = (float *)malloc((size_t)n * sizeof(float)), *yf = (float *)malloc((size_t)n * sizeof(float));
+  for (int64_t i = 0; i < n; ++i) xf[i] = (float)x[i];
+  oracle_rope_f32(xf, yf, B, L, H, D, theta);
+  for (int64_t i = 0; i < n; ++i) y[i] = (f16)yf[i];
+  free(xf);
+  free(yf);
+}
+
+/* ------------------------------------------------------------------ whole-vector sum
+ * sum_kernel, test/python/triton/test_sum.py:31-36: tl.sum over the block; the order of the
+ * reduction is unspecified, so the oracle sums exactly (double) and rounds once. */
+float oracle_sum_f32(const float *x, int64_t n) {
+  double s = 0.0;
+  for (int64_t i = 0; i < n; ++i) s += x[i];
+  return (float)s;
+}
+float oracle_sum_f16(const f16 *x, int64_t n) {
+  double s = 0.0;
+  for (int64_t i = 0; i < n; ++i) s += (double)x[i];
+  return (float)s;
+}
+
 /* out[r, c] = silu(gu[r, c]) * gu[r, cols + c], fp32 arithmetic, one rounding. */
 void oracle_swiglu_f16(const f16 *gu, f16 *out, int64_t rows, int64_t cols) {
 #pragma omp parallel for

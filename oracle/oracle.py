@@ -121,6 +121,45 @@ def c_silu(x):
     return y
 
 
+def c_gelu(x):
+    y = torch.empty_like(x)
+    fn = lib().oracle_gelu_f16 if x.dtype == torch.float16 else lib().oracle_gelu_f32
+    fn(_p(x), _p(y), _i64(x.numel()))
+    return y
+
+
+def c_rope(x, theta=10000.0):
+    y = torch.empty_like(x)
+    B, L, H, D = x.shape
+    fn = lib().oracle_rope_f16 if x.dtype == torch.float16 else lib().oracle_rope_f32
+    fn(_p(x), _p(y), _i64(B), _i64(L), _i64(H), _i64(D), C.c_float(theta))
+    return y
+
+
+def c_sum(x):
+    fn = lib().oracle_sum_f16 if x.dtype == torch.float16 else lib().oracle_sum_f32
+    fn.restype = C.c_float
+    return float(fn(_p(x), _i64(x.numel())))
+
+
+def torch_gelu(x):
+    return F.gelu(x.float(), approximate="tanh").to(x.dtype)
+
+
+def torch_rope(x, theta=10000.0):
+    """The PyTorch restatement the reference ships with its test (test_rope.py:58-92), in fp32."""
+    B, L, H, D = x.shape
+    idx = torch.arange(D, dtype=torch.float32)
+    steps = torch.where(idx % 2 == 0, idx, idx - 1)
+    freqs = 1.0 / (theta ** (steps / D))
+    ang = torch.arange(L, dtype=torch.float32)[:, None] * freqs[None, :]
+    cos, sin = torch.cos(ang).reshape(1, L, 1, D), torch.sin(ang).reshape(1, L, 1, D)
+    xf = x.float()
+    fwd, bwd = torch.roll(xf, -1, 3), torch.roll(xf, 1, 3)
+    even = (torch.arange(D) % 2 == 0).view(1, 1, 1, D)
+    return torch.where(even, xf * cos - fwd * sin, bwd * sin + xf * cos).to(x.dtype)
+
+
 def c_swiglu(gu):
     rows, c2 = gu.shape
     out = torch.empty(rows, c2 // 2, dtype=torch.float16)

@@ -8,7 +8,7 @@ The reference's test modules are imported unmodified with
     ``triton.runtime.driver.set_active`` (the real ones need the Hexagon toolchain),
   * ``parameterize_func_name`` (a rename of the kernel per dtype) made the identity, because the
     interpreter finds the kernel by its source name,
-  * ``torch.rand`` seeded and recorded, and ``torch.allclose`` wrapped to capture the kernel's
+  * ``torch.rand`` seeded and recorded, and ``torch.allclose`` / ``torch.testing.assert_close`` wrapped to capture the kernel's
     output and the torch reference the test compares it with.
 
 Each fixture ``<case>.npz`` holds the recorded inputs (in0, in1, ...), ``output`` (what the
@@ -48,31 +48,50 @@ class Recorder:
 
     def __init__(self, seed):
         self.inputs, self.output, self.expected = [], None, None
+        self.pairs = []  # every (output, expected) the test compared, in order
         self.seed = seed
 
     def __enter__(self):
         self._rand, self._allclose = torch.rand, torch.allclose
+        self._randn, self._linspace = torch.randn, torch.linspace
         torch.manual_seed(self.seed)
 
-        def rand(*a, **k):
-            t = self._rand(*a, **k)
-            self.inputs.append(t.clone())
-            return t
+        def recording(fn):
+            def wrapped(*a, **k):
+                t = fn(*a, **k)
+                self.inputs.append(t.clone())
+                return t
+            return wrapped
 
         def allclose(a, b, *rest, **k):
-            self.output, self.expected = a.clone(), b.clone()
+            self.output, self.expected = a.clone(), torch.as_tensor(b).clone()
+            self.pairs.append((self.output, self.expected))
             return self._allclose(a, b, *rest, **k)
 
-        torch.rand, torch.allclose = rand, allclose
+        torch.rand, torch.randn, torch.linspace = recording(self._rand), recording(self._randn), recording(self._linspace)
+        torch.allclose = allclose
+        self._assert_close = torch.testing.assert_close
+
+        def assert_close(a, b, *rest, **k):   # test_rope.py compares with torch.testing.assert_close
+            self.output, self.expected = a.clone(), torch.as_tensor(b).clone()
+            self.pairs.append((self.output, self.expected))
+            return self._assert_close(a, b, *rest, **k)
+
+        torch.testing.assert_close = assert_close
         return self
 
     def __exit__(self, *exc):
         torch.rand, torch.allclose = self._rand, self._allclose
+        torch.randn, torch.linspace = self._randn, self._linspace
+        torch.testing.assert_close = self._assert_close
 
     def save(self, name):
         arrays = {f"in{i}": t.numpy() for i, t in enumerate(self.inputs)}
         arrays["output"] = self.output.numpy()
         arrays["expected"] = self.expected.numpy()
+        if len(self.pairs) > 1:
+            for i, (o, e) in enumerate(self.pairs):
+                arrays[f"output{i}"], arrays[f"expected{i}"] = o.numpy(), e.numpy()
         np.savez_compressed(OUT / f"{name}.npz", **arrays)
         err = float((self.output.float() - self.expected.float()).abs().max())
         print(f"{name}: {len(self.inputs)} inputs, output {tuple(self.output.shape)} {self.output.dtype}, "
@@ -130,6 +149,42 @@ def main():
         with Recorder(17) as r:
             si.test_silu(16384, 4, dt, False, False)
         r.save(f"silu_16384_{tag}")
+
+    ge = mod("test_gelu")
+    for dt, tag in ((torch.float32, "f32"), (torch.float16, "f16")):
+        with Recorder(18) as r:
+            ge.test_gelu(16384, 4, dt, True)
+        r.save(f"gelu_16384_{tag}")
+
+    ro = mod("test_rope")
+    for dt, tag in ((torch.float32, "f32"), (torch.float16, "f16")):
+        with Recorder(19) as r:
+            ro.test_rope(4, dt)
+        r.save(f"rope_{ro.BATCH_SIZE}x{ro.SEQ_LEN}x{ro.N_HEADS}x{ro.N_FEATURES}_{tag}")
+
+    su = mod("test_sum")
+    with Recorder(20) as r:
+        su.test_vec_add(16384, torch.float32)   # the sum test (its function is named test_vec_add)
+    r.save("sum_16384_f32")
+
+    va = mod("test_vec_add")
+    va.BLOCK_SIZE = 4096                         # module-level size constant of the test; same kernel
+    with Recorder(21) as r:
+        va.test_vec_add()
+    r.save("vec_add_f32")
+
+    vd = mod("test_vec_div_2d")
+    vd.N_ROWS, vd.N_COLUMNS = 8, 512             # module-level shape constants of the test; same kernel
+    with Recorder(22) as r:
+        vd.test_vec_div()
+    r.save("vec_div_2d_f32")
+
+    mo = mod("test_math_ops")
+    with Recorder(23) as r:
+        mo.test_math_ops()                       # two comparisons: cos, then sin
+    r.save("math_ops_cos_sin_f32")
+    # test_rsqrt.py calls libdevice.rsqrt, which Triton's interpreter cannot execute: no fixture;
+    # the oracle for rsqrt is torch.rsqrt, the value that test asserts against.
 
 
 if __name__ == "__main__":

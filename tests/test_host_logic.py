@@ -184,3 +184,37 @@ def test_two_rank_shard_and_gather_gloo(rows):
         assert p.exitcode == 0
     assert all(ok for _, ok, _ in res)
     assert all(shape == (rows, 32) for _, _, shape in res)
+
+
+def test_raw_tensor_file_round_trip(tmp_path):
+    import struct
+
+    from hexb200 import report
+
+    for t in (torch.arange(24, dtype=torch.float32).reshape(2, 3, 4), torch.randn(5, 7).half(),
+              torch.tensor(3.5), torch.arange(6, dtype=torch.int64), torch.empty(0, 4)):
+        p = tmp_path / "t.raw"
+        report.dump_tensor(str(p), t)
+        back = report.load_tensor(str(p))
+        assert back.dtype == t.dtype and back.shape == t.shape and torch.equal(back, t)
+    # the header layout the reference's executor parses: u32 dtype id, i64 rank, i64 shape...
+    report.dump_tensor(str(p), torch.zeros(2, 5, dtype=torch.float16))
+    raw = p.read_bytes()
+    assert struct.unpack("I", raw[:4])[0] == 1 and struct.unpack("q", raw[4:12])[0] == 2
+    assert struct.unpack("qq", raw[12:28]) == (2, 5) and len(raw) == 28 + 20
+    report.dump_input(str(p), torch.arange(8, dtype=torch.float32))
+    assert torch.equal(report.load_input(str(p), torch.float32, (2, 4)), torch.arange(8.0).reshape(2, 4))
+    p.write_bytes(b"\x63\x00\x00\x00" + b"\x00" * 8)
+    with pytest.raises(ValueError):
+        report.load_tensor(str(p))
+
+
+def test_test_info_block():
+    from hexb200 import report
+
+    r = report.TestReport("softmax_kernel", 12.5, "us", "Pass")
+    assert r.text() == "Test_Info: {\n\tName:softmax_kernel\n\tResult:Pass\n\tPerf:12.500000\n\tUnits:us\n}\n"
+    back = report.TestReport.parse(r.text())
+    assert (back.name, back.perf, back.units, back.result) == ("softmax_kernel", 12.5, "us", "Pass")
+    with pytest.raises(ValueError):
+        report.TestReport("x", 1.0, "us", "Maybe")

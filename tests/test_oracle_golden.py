@@ -110,3 +110,36 @@ def test_decoder_oracles_agree():
     c = O.c_decoder(x.reshape(-1, 256), ws, 2, 128, 512, 2, 128, 1e-6).reshape(x.shape)
     t = O.torch_decoder(x, ws, 2, 128, 512, 2, 128, 1e-6)
     assert O.max_rel_err(c, t) < 2e-2
+
+
+# ------------------------------------------------------------------ elementwise row (gelu, rope, sum, add/div, cos/sin)
+@pytest.mark.parametrize("tag,atol", [("f32", 1e-5), ("f16", 1e-2)])
+def test_gelu_golden(golden_dir, tag, atol):
+    g = load(golden_dir, f"gelu_16384_{tag}")
+    for got in (O.c_gelu(g["in0"]), O.torch_gelu(g["in0"])):
+        assert torch.allclose(got, g["output"], atol=atol)
+        assert torch.allclose(got, g["expected"], atol=atol)
+
+
+@pytest.mark.parametrize("tag,atol", [("f32", 1e-3), ("f16", 1e-2)])
+def test_rope_golden(golden_dir, tag, atol):
+    g = load(golden_dir, f"rope_4x8x16x32_{tag}")
+    for got in (O.c_rope(g["in0"]), O.torch_rope(g["in0"])):
+        assert torch.allclose(got, g["output"], atol=atol, rtol=0)
+        assert torch.allclose(got, g["expected"], atol=atol, rtol=0)
+
+
+def test_sum_golden(golden_dir):
+    g = load(golden_dir, "sum_16384_f32")
+    assert abs(O.c_sum(g["in0"]) - float(g["output"])) < 1e-2
+    assert abs(O.c_sum(g["in0"]) - float(g["expected"])) < 1e-2
+
+
+def test_binary_and_math_golden(golden_dir):
+    g = load(golden_dir, "vec_add_f32")
+    assert torch.allclose(g["in0"] + g["in1"], g["output"])
+    g = load(golden_dir, "vec_div_2d_f32")
+    assert torch.allclose(g["in0"] / g["in1"], g["output"], atol=1e-6)
+    g = load(golden_dir, "math_ops_cos_sin_f32")
+    assert torch.allclose(torch.cos(g["in0"]), g["output0"], atol=1e-5)
+    assert torch.allclose(torch.sin(g["in0"]), g["output1"], atol=1e-5)
