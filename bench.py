@@ -576,7 +576,9 @@ def main():
             sc = 1e9 if w2.bound == "hbm" else 1e12
             extras[name] = {"value": round(w2.work_per_step() / (ms2 * 1e-3) / sc, 2), "unit": w2.unit,
                             "ms_per_step": round(ms2, 5), "steps": k2, "roofline": roofline(w2, ms2, peaks),
-                            "config": w2.describe(), "e2e": e2e_generic(w2, k2), "device_status": hexb200.device_status()}
+                            "config": w2.describe(), "device_status": hexb200.device_status(),
+                            "e2e": None if args.no_e2e else (e2e_layernorm(w2, k2) if name == "layernorm"
+                                                             else e2e_generic(w2, k2))}
             del w2
             torch.cuda.empty_cache()
         line["workloads"] = extras

@@ -355,6 +355,308 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_attn_status, (int)HEXB_ERR_TIMEOUT);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Second form of the tensor-core kernel: 64-wide key/value blocks with TWO score buffers.
+//
+// In the kernel above P aliases S, so Q.K^T of block j+1 cannot start before the softmax of block j
+// has finished: every stream is a serial chain MMA -> softmax -> MMA.  Here a block is 64 keys, so
+// two S buffers (2 x 64 columns) plus O (128) still fit 256 TMEM columns (two CTAs per SM), and two
+// K and two V tiles of 64 rows fit the same 96 KiB of shared memory.  The MMA thread issues
+// Q.K_{j+1}^T into the other S buffer before it waits for P_j, so the softmax warps find the next
+// scores ready when they finish a block and the tensor pipe works through Q.K^T / P.V while they
+// exponentiate.  P_j is written over the first 32 columns of S buffer j%2; Q.K_{j+2}^T, which
+// overwrites it, is issued after P_j.V_j (the tensor pipe retires in issue order).
+template <int HD>
+struct Cfg2 {
+  static constexpr int BN = 64;                       // keys per block
+  static constexpr int CHUNKS = HD / 64;
+  static constexpr int Q_BYTES = 128 * HD * 2;
+  static constexpr int Q_CHUNK = 128 * 128;           // 128 rows x 128 bytes
+  static constexpr int KV_BYTES = BN * HD * 2;
+  static constexpr int KV_CHUNK = BN * 128;           // 64 rows x 128 bytes
+  static constexpr int NBAR = 17;
+  static constexpr int NEEDED = Q_BYTES + 4 * KV_BYTES + NBAR * 8 + 16 + 1024;
+  static constexpr int SMEM_BYTES = NEEDED < 100 * 1024 ? 100 * 1024 : NEEDED;  // caps residency at 2 CTAs/SM
+  static constexpr int TMEM_COLS = 256;               // S0 [0,64), S1 [64,128), O [128,128+HD); P_b over S_b[0,32)
+  static constexpr int O_COL = 128;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 2)
+attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const Params p) {
+  using cfg = Cfg2<HD>;
+  constexpr int BN = cfg::BN;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = tc::smem_u32(smem_raw);
+  const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+  uint8_t *smem = smem_raw + pad;
+  const uint32_t smem_addr = raw_addr + pad;
+  const uint32_t sQ = smem_addr;
+  const uint32_t sK0 = sQ + cfg::Q_BYTES, sV0 = sK0 + 2 * cfg::KV_BYTES;
+  const uint32_t bar0 = sV0 + 2 * cfg::KV_BYTES;
+  const uint32_t q_full = bar0, q_empty = bar0 + 8, o_full = bar0 + 16, o_empty = bar0 + 24, pv_done = bar0 + 32;
+  auto k_full = [&](uint32_t b) { return bar0 + 40 + 8 * b; };
+  auto k_empty = [&](uint32_t b) { return bar0 + 56 + 8 * b; };
+  auto v_full = [&](uint32_t b) { return bar0 + 72 + 8 * b; };
+  auto v_empty = [&](uint32_t b) { return bar0 + 88 + 8 * b; };
+  auto s_full = [&](uint32_t b) { return bar0 + 104 + 8 * b; };
+  // p_full[2] follow at +120 (NBAR = 15 counts q_full..s_full; two more for p_full)
+  auto p_full = [&](uint32_t b) { return bar0 + 120 + 8 * b; };
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + cfg::Q_BYTES + 4 * cfg::KV_BYTES + 136);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int bh = blockIdx.x / p.ctas_per_bh;
+  const int q_rank = blockIdx.x - bh * p.ctas_per_bh;
+  const int z = bh / p.H, h = bh - z * p.H;
+  const int kv_blocks = (p.N_CTX + BN - 1) / BN;
+  auto tile_of = [&](int t) {
+    if (p.causal) return t == 0 ? p.num_q_tiles - 1 - q_rank : q_rank;
+    return q_rank * p.tiles_per_cta + t;
+  };
+  // causal: keys 0 .. m0+127 -> 2*(q_tile+1) blocks of 64
+  auto nkv_of = [&](int q_tile) {
+    const int need = 2 * (q_tile + 1);
+    return (p.causal && need < kv_blocks) ? need : kv_blocks;
+  };
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(q_full, 1);
+    tc::mbar_init(q_empty, 1);
+    tc::mbar_init(o_full, 1);
+    tc::mbar_init(o_empty, 4);
+    tc::mbar_init(pv_done, 1);
+    for (uint32_t b = 0; b < 2; ++b) {
+      tc::mbar_init(k_full(b), 1);
+      tc::mbar_init(k_empty(b), 1);
+      tc::mbar_init(v_full(b), 1);
+      tc::mbar_init(v_empty(b), 1);
+      tc::mbar_init(s_full(b), 1);
+      tc::mbar_init(p_full(b), 4);
+    }
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::prefetch_tensormap(&tmQ);
+    tc::prefetch_tensormap(&tmK);
+    tc::prefetch_tensormap(&tmV);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tc::smem_u32(tmem_slot), cfg::TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tO = tmem_base + cfg::O_COL;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
+        const int q_tile = tile_of(t);
+        const int n_kv = nkv_of(q_tile);
+        if (t > 0 && !tc::mbar_wait(q_empty, (uint32_t)(t - 1) & 1u, abort_flag)) break;
+        tc::mbar_arrive_expect_tx(q_full, cfg::Q_BYTES);
+#pragma unroll
+        for (int c = 0; c < cfg::CHUNKS; ++c)
+          tc::tma_load_4d(sQ + c * cfg::Q_CHUNK, &tmQ, c * 64, q_tile * BLOCK_M, h, z, q_full);
+        for (int j = 0; j < n_kv; ++j, ++it) {
+          const uint32_t b = it & 1u, ph = (it >> 1) & 1u;
+          if (!tc::mbar_wait(k_empty(b), ph ^ 1u, abort_flag)) { ok = false; break; }
+          tc::mbar_arrive_expect_tx(k_full(b), cfg::KV_BYTES);
+#pragma unroll
+          for (int c = 0; c < cfg::CHUNKS; ++c)
+            tc::tma_load_4d(sK0 + b * cfg::KV_BYTES + c * cfg::KV_CHUNK, &tmK, c * 64, j * BN, h, z, k_full(b));
+          if (!tc::mbar_wait(v_empty(b), ph ^ 1u, abort_flag)) { ok = false; break; }
+          tc::mbar_arrive_expect_tx(v_full(b), cfg::KV_BYTES);
+#pragma unroll
+          for (int c = 0; c < cfg::CHUNKS; ++c)
+            tc::tma_load_4d(sV0 + b * cfg::KV_BYTES + c * cfg::KV_CHUNK, &tmV, c * 64, j * BN, h, z, v_full(b));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = tc::make_idesc_f16_f32(BLOCK_M, BN, 0, 0);
+      constexpr uint32_t idesc_pv = tc::make_idesc_f16_f32(BLOCK_M, HD, 0, 1);
+      bool ok = true;
+      // S_{blk} = Q . K_{blk}^T into score buffer blk % 2
+      auto issue_qk = [&](uint32_t blk, bool last_of_tile) {
+        const uint32_t b = blk & 1u, ph = (blk >> 1) & 1u;
+        if (!tc::mbar_wait(k_full(b), ph, abort_flag)) { ok = false; return; }
+        tc::tc_fence_after();
+        const uint32_t sK = sK0 + b * cfg::KV_BYTES;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t qoff = (uint32_t)((k >> 2) * cfg::Q_CHUNK + (k & 3) * 32);
+          const uint32_t koff = (uint32_t)((k >> 2) * cfg::KV_CHUNK + (k & 3) * 32);
+          tc::mma_f16_ss(tmem_base + b * BN, tc::make_smem_desc_sw128(sQ + qoff, 16, 1024),
+                         tc::make_smem_desc_sw128(sK + koff, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
+        }
+        tc::mma_commit(s_full(b));
+        tc::mma_commit(k_empty(b));
+        if (last_of_tile) tc::mma_commit(q_empty);
+      };
+      uint32_t it = 0;
+      for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
+        const int n_kv = nkv_of(tile_of(t));
+        if (!tc::mbar_wait(q_full, (uint32_t)t & 1u, abort_flag)) break;
+        issue_qk(it, n_kv == 1);
+        for (int j = 0; j < n_kv && ok; ++j, ++it) {
+          if (j + 1 < n_kv) issue_qk(it + 1, j + 2 == n_kv);  // run one block ahead of the softmax
+          if (!ok) break;
+          const uint32_t b = it & 1u, ph = (it >> 1) & 1u;
+          if (!tc::mbar_wait(p_full(b), ph, abort_flag)) { ok = false; break; }
+          if (!tc::mbar_wait(v_full(b), ph, abort_flag)) { ok = false; break; }
+          // the first product of a later tile overwrites O: the previous epilogue must have read it
+          if (j == 0 && t > 0 && !tc::mbar_wait(o_empty, (uint32_t)(t - 1) & 1u, abort_flag)) { ok = false; break; }
+          tc::tc_fence_after();
+          const uint32_t sV = sV0 + b * cfg::KV_BYTES;
+#pragma unroll
+          for (int k = 0; k < BN / 16; ++k) {
+            tc::mma_f16_ts(tO, tmem_base + b * BN + (uint32_t)(k * 8),
+                           tc::make_smem_desc_sw128(sV + (uint32_t)(k * 2048), cfg::KV_CHUNK, 1024), idesc_pv,
+                           (j | k) != 0 ? 1u : 0u);
+          }
+          tc::mma_commit(v_empty(b));
+          tc::mma_commit(pv_done);
+          if (j == n_kv - 1) tc::mma_commit(o_full);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax / correction / epilogue
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
+      const int q_tile = tile_of(t);
+      const int n_kv = nkv_of(q_tile);
+      const int m0 = q_tile * BLOCK_M;
+      const int qi = m0 + r;
+      float m_ref = -INFINITY, l = 0.f;
+      for (int j = 0; j < n_kv; ++j, ++it) {
+        const uint32_t b = it & 1u, ph = (it >> 1) & 1u;
+        if (!tc::mbar_wait(s_full(b), ph, abort_flag)) { ok = false; break; }
+        tc::tc_fence_after();
+        const uint32_t tS = tmem_base + b * BN, tP = tS;
+        const int kv0 = j * BN;
+        const bool need_mask = (p.causal && kv0 + BN - 1 > m0) || (kv0 + BN > p.N_CTX);
+        uint32_t sv[BN];
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c)
+          tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c * 32), reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
+        tc::tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < BN; ++e) {
+            const int kv = kv0 + e;
+            if ((p.causal && kv > qi) || kv >= p.N_CTX) sv[e] = 0xff800000u;
+          }
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int e = 0; e < BN; e += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mx4[u] = max3(mx4[u], __uint_as_float(sv[e + 2 * u]), __uint_as_float(sv[e + 2 * u + 1]));
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+        const float m_new = fmaxf(m_ref, mx);
+        if (j == 0) {
+          m_ref = m_new;
+        } else if (__any_sync(0xffffffffu, m_new - m_ref > kRescaleThreshold)) {
+          // O must be quiescent: P_{it-1}.V_{it-1} is the it-th completion of pv_done
+          if (!tc::mbar_wait(pv_done, (it - 1u) & 1u, abort_flag)) { ok = false; break; }
+          tc::tc_fence_after();
+          const float alpha = ex2_approx(m_ref - m_new);
+          m_ref = m_new;
+          l *= alpha;
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tc::tmem_st_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+          }
+        }
+        const float neg_m = -m_ref;
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + e]), p.scale_log2, neg_m));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + e + 1]), p.scale_log2, neg_m));
+            l0 += p0;
+            l1 += p1;
+            pk[e >> 1] = pack_f16x2(p0, p1);
+          }
+          tc::tmem_st_32x16(tP + lane_off + (uint32_t)(c * 16), pk);
+        }
+        l += l0 + l1;
+        tc::tmem_st_wait();
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(p_full(b));
+      }
+      if (!ok || !tc::mbar_wait(o_full, (uint32_t)t & 1u, abort_flag)) { ok = false; break; }
+      tc::tc_fence_after();
+      const float inv = 1.0f / l;
+      __half *orow = p.out + (int64_t)z * p.so_z + (int64_t)h * p.so_h + (int64_t)qi * p.so_n;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+        tc::tmem_ld_wait();
+        if (c == HD / 32 - 1) {
+          tc::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(o_empty);
+        }
+        if (qi < p.N_CTX) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[g * 8 + e]) * inv;
+            if (p.out_vec_ok) {
+              Vec16<__half> ov;
+              ov.pack(f);
+              *reinterpret_cast<uint4 *>(orow + c * 32 + g * 8) = ov.raw;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) orow[c * 32 + g * 8 + e] = __float2half_rn(f[e]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, cfg::TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_attn_status, (int)HEXB_ERR_TIMEOUT);
+}
+
 // CUDA-core forward for fp32 tensors and for shapes the TMA path cannot take: one warp per query
 // row, 32 keys per step (one per lane), base-2 online softmax exactly as _attn_fwd_inner writes it
 // (running max of scaled scores, alpha = exp2(m_old - m_new)); each lane owns D/32 output columns.
@@ -444,21 +746,23 @@ template <int HD>
 static int launch_tc(const __half *Q, const __half *K, const __half *V, __half *O, int64_t Z, int64_t H,
                      int64_t N, const int64_t *s, float scale_log2, int causal, cudaStream_t st) {
   using cfg = Cfg<HD>;
+  const bool two_buffers = option("attn_kernel", 2) == 2;  // 2: 64-key blocks, two score buffers; 1: 128-key blocks
   CUtensorMap tm[3];
   const __half *base[3] = {Q, K, V};
   for (int i = 0; i < 3; ++i) {
     const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)N, (uint64_t)H, (uint64_t)Z};
     const uint64_t strides[3] = {(uint64_t)s[3 * i + 2] * 2, (uint64_t)s[3 * i + 1] * 2,
                                  (uint64_t)s[3 * i + 0] * 2};
-    const uint32_t box[4] = {64, 128, 1, 1};
+    const uint32_t box[4] = {64, (i > 0 && two_buffers) ? 64u : 128u, 1, 1};
     if (int e = encode_tmap_f16_sw128(&tm[i], base[i], 4, dims, strides, box)) return e;
   }
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = attn_fwd_tc_kernel<HD>;
   if (!attr_done[dev & 63]) {
-    HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
+    HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
+    HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg2<HD>::SMEM_BYTES));
     attr_done[dev & 63] = true;
   }
   Params p;
@@ -476,7 +780,10 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, __half *
   p.ctas_per_bh = p.num_q_tiles / p.tiles_per_cta;
   const int64_t ctas = (int64_t)p.ctas_per_bh * Z * H;
   if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
-  kern<<<(unsigned)ctas, THREADS, cfg::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2], p);
+  if (two_buffers)
+    attn_fwd_tc2_kernel<HD><<<(unsigned)ctas, THREADS, Cfg2<HD>::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2], p);
+  else
+    attn_fwd_tc_kernel<HD><<<(unsigned)ctas, THREADS, cfg::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2], p);
   return check_launch("attn_tc");
 }
 
