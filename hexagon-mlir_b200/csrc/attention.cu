@@ -81,7 +81,23 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   return r;
 }
 
+// Phase timing for development builds (-DHEXB_ATTN_PROFILE): clock64 stamps around the phases of
+// one softmax warp and of the MMA thread of attn_fwd_tc2_kernel, summed into a device buffer that
+// hexb_debug_set_attn_profile() registers.  Compiled out otherwise.
+#ifdef HEXB_ATTN_PROFILE
+#define HEXB_PROF_DECL(n) long long prof_t[n] = {}; long long prof_last = clock64();
+#define HEXB_PROF(i) { const long long now_ = clock64(); prof_t[i] += now_ - prof_last; prof_last = now_; }
+#define HEXB_PROF_FLUSH(base, n) if (p.prof) { for (int i_ = 0; i_ < n; ++i_) atomicAdd(p.prof + base + i_, (unsigned long long)prof_t[i_]); }
+#else
+#define HEXB_PROF_DECL(n)
+#define HEXB_PROF(i)
+#define HEXB_PROF_FLUSH(base, n)
+#endif
+
 struct Params {
+#ifdef HEXB_ATTN_PROFILE
+  unsigned long long *prof;
+#endif
   __half *out;
   int64_t so_z, so_h, so_n;
   int Z, H, N_CTX;
@@ -487,9 +503,12 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       constexpr uint32_t idesc_pv = tc::make_idesc_f16_f32(BLOCK_M, HD, 0, 1);
       bool ok = true;
       // S_{blk} = Q . K_{blk}^T into score buffer blk % 2
+      HEXB_PROF_DECL(8)
       auto issue_qk = [&](uint32_t blk, bool last_of_tile) {
         const uint32_t b = blk & 1u, ph = (blk >> 1) & 1u;
+        HEXB_PROF(0)  // other
         if (!tc::mbar_wait(k_full(b), ph, abort_flag)) { ok = false; return; }
+        HEXB_PROF(1)  // wait K
         tc::tc_fence_after();
         const uint32_t sK = sK0 + b * cfg::KV_BYTES;
 #pragma unroll
@@ -502,6 +521,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc::mma_commit(s_full(b));
         tc::mma_commit(k_empty(b));
         if (last_of_tile) tc::mma_commit(q_empty);
+        HEXB_PROF(2)  // issue QK
       };
       uint32_t it = 0;
       for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
@@ -513,7 +533,9 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (!ok) break;
           const uint32_t b = it & 1u, ph = (it >> 1) & 1u;
           if (!tc::mbar_wait(p_full(b), ph, abort_flag)) { ok = false; break; }
+          HEXB_PROF(3)  // wait P
           if (!tc::mbar_wait(v_full(b), ph, abort_flag)) { ok = false; break; }
+          HEXB_PROF(4)  // wait V
           // the first product of a later tile overwrites O: the previous epilogue must have read it
           if (j == 0 && t > 0 && !tc::mbar_wait(o_empty, (uint32_t)(t - 1) & 1u, abort_flag)) { ok = false; break; }
           tc::tc_fence_after();
@@ -527,8 +549,10 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tc::mma_commit(v_empty(b));
           tc::mma_commit(pv_done);
           if (j == n_kv - 1) tc::mma_commit(o_full);
+          HEXB_PROF(5)  // issue PV
         }
       }
+      HEXB_PROF_FLUSH(0, 8)
     }
   } else {
     // ------------------------------------------------------------ softmax / correction / epilogue
@@ -537,6 +561,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     uint32_t it = 0;
     bool ok = true;
+    HEXB_PROF_DECL(8)
     for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
       const int q_tile = tile_of(t);
       const int n_kv = nkv_of(q_tile);
@@ -545,7 +570,9 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       float m_ref = -INFINITY, l = 0.f;
       for (int j = 0; j < n_kv; ++j, ++it) {
         const uint32_t b = it & 1u, ph = (it >> 1) & 1u;
+        HEXB_PROF(0)  // loop / epilogue of the previous tile
         if (!tc::mbar_wait(s_full(b), ph, abort_flag)) { ok = false; break; }
+        HEXB_PROF(1)  // wait S
         tc::tc_fence_after();
         const uint32_t tS = tmem_base + b * BN, tP = tS;
         const int kv0 = j * BN;
@@ -555,6 +582,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int c = 0; c < BN / 32; ++c)
           tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c * 32), reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
         tc::tmem_ld_wait();
+        HEXB_PROF(2)  // TMEM load of S
         if (need_mask) {
 #pragma unroll
           for (int e = 0; e < BN; ++e) {
@@ -590,6 +618,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tc::tmem_st_32x32(tO + lane_off + (uint32_t)(c * 32), o);
           }
         }
+        HEXB_PROF(3)  // mask, max, rescale
         const float neg_m = -m_ref;
         float l0 = 0.f, l1 = 0.f;
 #pragma unroll
@@ -606,10 +635,12 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tc::tmem_st_32x16(tP + lane_off + (uint32_t)(c * 16), pk);
         }
         l += l0 + l1;
+        HEXB_PROF(4)  // exp, pack, TMEM store issue
         tc::tmem_st_wait();
         tc::tc_fence_before();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(p_full(b));
+        HEXB_PROF(5)  // store wait + arrive
       }
       if (!ok || !tc::mbar_wait(o_full, (uint32_t)t & 1u, abort_flag)) { ok = false; break; }
       tc::tc_fence_after();
@@ -642,7 +673,9 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
       }
+      HEXB_PROF(6)  // epilogue
     }
+    if (threadIdx.x == 64) { HEXB_PROF_FLUSH(8, 8) }
   }
 
   if (*abort_flag) {
@@ -656,6 +689,11 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_attn_status, (int)HEXB_ERR_TIMEOUT);
 }
+
+#ifdef HEXB_ATTN_PROFILE
+static unsigned long long *g_attn_prof = nullptr;
+extern "C" void hexb_debug_set_attn_profile(void *dev_buf) { g_attn_prof = (unsigned long long *)dev_buf; }
+#endif
 
 // CUDA-core forward for fp32 tensors and for shapes the TMA path cannot take: one warp per query
 // row, 32 keys per step (one per lane), base-2 online softmax exactly as _attn_fwd_inner writes it
@@ -766,6 +804,9 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, __half *
     attr_done[dev & 63] = true;
   }
   Params p;
+#ifdef HEXB_ATTN_PROFILE
+  p.prof = g_attn_prof;
+#endif
   p.out = O;
   p.so_z = s[9]; p.so_h = s[10]; p.so_n = s[11];
   p.Z = (int)Z; p.H = (int)H; p.N_CTX = (int)N;

@@ -11,7 +11,7 @@
 //
 // Heads are split and merged by strides inside the attention call (q|k|v column blocks of the
 // QKV product, head-major inside each block); no transposes.  The residual adds ride in the
-// epilogue of the Wo and Wd products.
+// epilogue of the Wo and Wd products, the SwiGLU gating in the epilogue of the gate/up product.
 #include <mutex>
 
 #include "common.cuh"
@@ -87,8 +87,12 @@ extern "C" int hexb_decoder_forward_f16(const hexb_decoder_config *cfg, const he
       return s;
     if ((s = hexb_matmul_f16(attn, w->wo[l], h, xin, T, d, d, d, d, d, HEXB_DT_F16, stream))) return s;
     if ((s = hexb_rms_norm_f16(h, n, w->g2[l], T, d, d, d, cfg->rms_eps, stream))) return s;
-    if ((s = hexb_matmul_f16(n, w->wgu[l], gu, nullptr, T, 2 * f, d, d, 2 * f, 2 * f, HEXB_DT_F16, stream))) return s;
-    if ((s = hexb_swiglu_f16(gu, act, T, f, stream))) return s;
+    if (option("decoder_fused_swiglu", 1)) {
+      if ((s = hexb_matmul_swiglu_f16(n, w->wgu[l], act, T, f, d, d, 2 * f, f, stream))) return s;
+    } else {
+      if ((s = hexb_matmul_f16(n, w->wgu[l], gu, nullptr, T, 2 * f, d, d, 2 * f, 2 * f, HEXB_DT_F16, stream))) return s;
+      if ((s = hexb_swiglu_f16(gu, act, T, f, stream))) return s;
+    }
     if ((s = hexb_matmul_f16(act, w->wd[l], xout, h, T, d, f, f, d, d, HEXB_DT_F16, stream))) return s;
     xin = xout;
   }

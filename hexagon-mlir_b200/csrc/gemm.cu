@@ -97,7 +97,10 @@ __device__ __forceinline__ void store_row_chunk<float>(float *crow, const __half
   }
 }
 
-template <int BN, int STAGES, typename OutT>
+// EPI == 1 (SwiGLU, BN = 256, fp16 out): B is a [K, 2*N] gate|up matrix; a tile's B operand is made
+// of 128 gate columns [col0, col0+128) and the 128 up columns [N+col0, N+col0+128), so accumulator
+// columns c and 128+c belong to output column col0+c and the epilogue writes silu(gate) * up.
+template <int BN, int STAGES, typename OutT, int EPI = 0>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
@@ -163,7 +166,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       it.width = BN / split;
     }
     it.tm = tile % tiles_m;
-    it.col0 = (tile / tiles_m) * BN + sub * it.width;
+    it.col0 = (tile / tiles_m) * (EPI == 1 ? BN / 2 : BN) + sub * it.width;
     return it;
   };
 
@@ -183,8 +186,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(A_BYTES + chunks * BK * 128));
           tc::tma_load_2d(sa, &tmA, kb * BK, w.tm * BM, full_bar(stage));
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            if (j < chunks) tc::tma_load_2d(sb + j * (BK * 128), &tmB, w.col0 + j * 64, kb * BK, full_bar(stage));
+          for (int j = 0; j < BN / 64; ++j) {
+            int x = w.col0 + j * 64;
+            if (EPI == 1 && j >= BN / 128) x = N + w.col0 + (j - BN / 128) * 64;  // the matching up columns
+            if (j < chunks) tc::tma_load_2d(sb + j * (BK * 128), &tmB, x, kb * BK, full_bar(stage));
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -235,13 +241,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
       OutT *crow = C + (int64_t)row * ldc;
       const __half *rrow = R ? R + (int64_t)row * ldr : nullptr;
+      if constexpr (EPI == 1) {
 #pragma unroll 1
-      for (int c = 0; c < w.width / 32; ++c) {
-        uint32_t v[32];
-        tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
-        tc::tmem_ld_wait();
-        const int col0 = w.col0 + c * 32;
-        if (row < M && col0 < N) store_row_chunk<OutT>(crow, rrow, v, col0, N, vec_ok != 0);
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), g);
+          tc::tmem_ld_32x32(taddr + (uint32_t)(BN / 2 + c * 32), u);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float gv = __uint_as_float(g[e]);
+            g[e] = __float_as_uint((gv / (1.0f + __expf(-gv))) * __uint_as_float(u[e]));
+          }
+          const int col0 = w.col0 + c * 32;
+          if (row < M && col0 < N) store_row_chunk<OutT>(crow, nullptr, g, col0, N, vec_ok != 0);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < w.width / 32; ++c) {
+          uint32_t v[32];
+          tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
+          tc::tmem_ld_wait();
+          const int col0 = w.col0 + c * 32;
+          if (row < M && col0 < N) store_row_chunk<OutT>(crow, rrow, v, col0, N, vec_ok != 0);
+        }
       }
       tc::tc_fence_before();
       __syncwarp();
@@ -287,7 +310,7 @@ gemm_simt_kernel(const __half *__restrict__ A, const __half *__restrict__ B, Out
   }
 }
 
-template <int BN, int STAGES, typename OutT>
+template <int BN, int STAGES, typename OutT, int EPI = 0>
 static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M,
                      int N, int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count,
                      cudaStream_t st) {
@@ -295,17 +318,18 @@ static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, co
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = gemm_tc_kernel<BN, STAGES, OutT>;
+  auto kern = gemm_tc_kernel<BN, STAGES, OutT, EPI>;
   if (!attr_done[dev & 63]) {
     HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
     attr_done[dev & 63] = true;
   }
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;  // output columns per tile
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
   const int tiles = tiles_m * tiles_n;
   // split the tiles of the last partial wave into column slices (>= 64 wide) while they still fit one wave
   int full_items = tiles / sm_count * sm_count, split = 1;
   const int rem = tiles - full_items;
-  if (rem > 0 && option("gemm_tail_split", 1)) {
+  if (EPI == 0 && rem > 0 && option("gemm_tail_split", 1)) {
     while (split * 2 <= BN / 64 && rem * split * 2 <= sm_count) split *= 2;
   }
   if (split == 1) full_items = tiles;
@@ -391,6 +415,36 @@ extern "C" int hexb_matmul_f16(const void *A, const void *B, void *C, const void
                                      (const __half *)residual, M, N, K, lda, ldb, ldc, (cudaStream_t)stream);
   return gemm::matmul_impl<float>((const __half *)A, (const __half *)B, (float *)C,
                                   (const __half *)residual, M, N, K, lda, ldb, ldc, (cudaStream_t)stream);
+}
+
+extern "C" int hexb_matmul_swiglu_f16(const void *A, const void *B_gate_up, void *out, int64_t M, int64_t F,
+                                      int64_t K, int64_t lda, int64_t ldb, int64_t ldo, void *stream) {
+  using namespace hexb;
+  using namespace hexb::gemm;
+  if (M < 0 || F < 0 || K < 0) return HEXB_ERR_BAD_ARG;
+  if (M == 0 || F == 0) return HEXB_OK;
+  if (!A || !B_gate_up || !out || K == 0) return HEXB_ERR_BAD_ARG;
+  if (lda < K || ldb < 2 * F || ldo < F) return HEXB_ERR_BAD_ARG;
+  if (lda % 8 || ldb % 8 || F % 8 || !aligned16(A) || !aligned16(B_gate_up)) return HEXB_ERR_MISALIGNED;
+  if (M >= (1ll << 31) || F >= (1ll << 30) || K >= (1ll << 31)) return HEXB_ERR_UNSUPPORTED;
+  DeviceInfo di;
+  if (int s = current_device(&di)) return s;
+  CUtensorMap tmA, tmB;
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t strides[1] = {(uint64_t)lda * 2};
+    const uint32_t box[2] = {BK, BM};
+    if (int s = encode_tmap_f16_sw128(&tmA, A, 2, dims, strides, box)) return s;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)(2 * F), (uint64_t)K};
+    const uint64_t strides[1] = {(uint64_t)ldb * 2};
+    const uint32_t box[2] = {64, BK};
+    if (int s = encode_tmap_f16_sw128(&tmB, B_gate_up, 2, dims, strides, box)) return s;
+  }
+  const int vec_ok = (ldo % 8 == 0) && aligned16(out);
+  return launch_tc<256, 4, __half, 1>(tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
+                                      di.sm_count, (cudaStream_t)stream);
 }
 
 extern "C" int hexkl_matmul_f16f16_f32(int64_t n_row, int64_t n_col, int64_t n_inner, float *outM,

@@ -159,6 +159,22 @@ def matmul(a, b, c, residual=None) -> None:
         check(lib.hexb_matmul_f16_host(_ptr(a), _ptr(b), _ptr(c), M, N, K, _dt(c)), "matmul_host")
 
 
+def matmul_swiglu(a, b_gate_up, out) -> None:
+    """out = silu(a @ b[:, :F]) * (a @ b[:, F:]) for a [M, K], b [K, 2F], out [M, F]; float16 CUDA tensors."""
+    lib = _lib.load()
+    _same_place(a, b_gate_up, out)
+    if not (a.dtype == b_gate_up.dtype == out.dtype == torch.float16):
+        raise TypeError("matmul_swiglu: float16 tensors expected")
+    M, K, lda = _rows2d(a, "A")
+    K2, F2, ldb = _rows2d(b_gate_up, "B")
+    M2, Fo, ldo = _rows2d(out, "out")
+    if K != K2 or M != M2 or F2 != 2 * Fo:
+        raise ValueError("matmul_swiglu: shapes do not agree")
+    with torch.cuda.device(a.device):
+        check(lib.hexb_matmul_swiglu_f16(_ptr(a), _ptr(b_gate_up), _ptr(out), M, Fo, K, lda, ldb, ldo, _stream(a)),
+              "matmul_swiglu")
+
+
 def hexkl_matmul_f16f16_f32(n_row, n_col, n_inner, out, act, w) -> None:
     """The HexKL runtime symbol, same argument order (bin/runtime/include/HexKLAPI.h:16-21); device tensors."""
     lib = _lib.load()

@@ -88,6 +88,14 @@ int hexb_matmul_f16(const void *A, const void *B, void *C, const void *residual,
                     int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int out_dtype,
                     void *stream);
 
+/* Gate/up projection with the SwiGLU gating fused into the epilogue:
+ *   out[M, F] = silu(A @ B[:, 0:F]) * (A @ B[:, F:2F]),  B = [K, 2F] row-major (columns gate|up).
+ * fp32 accumulation and gating, one rounding to fp16.  Composed from matmul
+ * (test/python/triton/test_matmul.py:35-70) and silu_kernel (test/python/triton/test_silu.py:38-52);
+ * the reference has no fused form.  Requires F, lda, ldb multiples of 8 and 16-byte aligned A, B. */
+int hexb_matmul_swiglu_f16(const void *A, const void *B_gate_up, void *out, int64_t M, int64_t F,
+                           int64_t K, int64_t lda, int64_t ldb, int64_t ldo, void *stream);
+
 /* Symbol-level drop-in for the HexKL runtime call: same name, argument order (rows, cols, inner,
  * out first) and fp32 output; device pointers, legacy default stream.
  * Replaces: hexkl_matmul_f16f16_f32 (qcom_hexagon_backend/bin/runtime/include/HexKLAPI.h:16-21). */

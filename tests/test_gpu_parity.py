@@ -462,3 +462,41 @@ def test_error_codes(dev):
     assert e.value.status_name == "HEXB_ERR_BAD_ARG"
     with pytest.raises(ValueError):
         ops.softmax(x, torch.zeros(4, 16, device=dev))
+
+
+# ------------------------------------------------------------------ gate/up projection with fused SwiGLU
+@pytest.mark.parametrize("M,F,K", [(128, 128, 64), (256, 384, 192), (300, 264, 136), (1000, 72, 40), (2048, 8192, 2048)])
+def test_matmul_swiglu_vs_oracle(dev, M, F, K):
+    g = torch.Generator().manual_seed(M + F + K)
+    a = (torch.randn(M, K, generator=g) * 0.5).half()
+    b = (torch.randn(K, 2 * F, generator=g) * K ** -0.5).half()
+    out = torch.empty(M, F, dtype=torch.float16, device=dev)
+    ops.matmul_swiglu(a.to(dev), b.to(dev), out)
+    torch.cuda.synchronize()
+    assert hexb200.device_status() == 0
+    rows = torch.arange(M) if M * F * K <= 1 << 26 else torch.tensor([0, 1, 127, 128, M // 2, M - 1])
+    gu = a[rows].float() @ b.float()
+    ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    assert O.max_rel_err(out.cpu()[rows], ref) < REL_F16
+    if M * F * K <= 1 << 24:
+        unfused = O.c_swiglu(O.c_matmul(a, b))                       # gate|up rounded to fp16 in between
+        assert O.max_rel_err(out.cpu(), unfused) < REL_F16
+
+
+def test_decoder_fused_and_unfused_gating_agree(dev):
+    L, d, H, f, B, S = 2, 256, 2, 512, 2, 128
+    x, ws = O.make_decoder_inputs(L, d, H, f, B, S, seed=77)
+    wd = [{k: v.to(dev) for k, v in w.items()} for w in ws]
+    stack = ops.DecoderStack(wd, H, d // H, f, B, S, 1e-6)
+    outs = []
+    try:
+        for fused in (1, 0):
+            hexb200.set_option("decoder_fused_swiglu", fused)
+            out = torch.empty(B, S, d, dtype=torch.float16, device=dev)
+            stack.forward(x.to(dev), out)
+            outs.append(out.cpu())
+    finally:
+        hexb200.set_option("decoder_fused_swiglu", 1)
+    assert O.max_rel_err(outs[0], outs[1]) < 5e-3
+    ref = O.torch_decoder(x, ws, H, d // H, f, B, S, 1e-6)
+    assert O.max_rel_err(outs[0], ref) < REL_F16 and O.max_rel_err(outs[1], ref) < REL_F16
