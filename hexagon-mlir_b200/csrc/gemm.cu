@@ -310,6 +310,207 @@ gemm_simt_kernel(const __half *__restrict__ A, const __half *__restrict__ B, Out
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair form (cta_group::2): a cluster of two CTAs computes a 256 x 256 tile.  Each CTA loads
+// its own 128 rows of A and its own half (128 columns) of the B tile, so per k-block a CTA writes
+// 32 KiB into shared memory instead of 48 and the tensor cores read each B half once for both CTAs;
+// six pipeline stages fit.  The leader CTA (cluster rank 0) issues the 256 x 256 x 16 MMAs; their
+// completion is multicast to the stage barriers of both CTAs; each CTA's epilogue warps drain their
+// own 128 accumulator rows and signal the leader when the buffer is free.  Every wait is bounded
+// and both CTAs meet at a cluster barrier before they exit.
+namespace pair {
+constexpr int STAGES = 6;
+constexpr int BN = 256;
+constexpr int B_HALF_BYTES = BK * 128 * 2;             // this CTA's 128 columns of the B tile: 16 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_HALF_BYTES;    // 32 KiB
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+constexpr int TMEM_COLS = 512;
+}  // namespace pair
+
+template <typename OutT, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
+                    int64_t ldr, int tiles_m, int tiles_n, int vec_ok) {
+  using namespace pair;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = tc::smem_u32(smem_raw);
+  const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+  uint8_t *smem = smem_raw + pad;
+  const uint32_t smem_addr = raw_addr + pad;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+  const uint32_t bar0 = smem_addr + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };                   // used in the leader only
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };       // one per CTA
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };   // one per CTA
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };  // used in the leader only
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = tc::cluster_ctarank();
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tc::mbar_init(full_bar(s), 1);
+      tc::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      tc::mbar_init(tfull_bar(a), 1);
+      tc::mbar_init(tempty_bar(a), 8);  // four epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::prefetch_tensormap(&tmA);
+    tc::prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc_pair(tc::smem_u32(tmem_slot), TMEM_COLS);
+    tc::tmem_relinquish_pair();
+  }
+  tc::tc_fence_before();
+  tc::cluster_sync_all();  // barriers of both CTAs are initialised before anything signals them
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
+  const int num_tiles = tiles_m * tiles_n;       // tiles of 256 rows x OUT_COLS output columns
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int tm = tile % tiles_m, col0 = (tile / tiles_m) * OUT_COLS;
+        const int row0 = tm * 256 + (int)rank * BM;
+        // this CTA's half of the B tile: plain = columns [col0 + 128*rank, +128);
+        // SwiGLU = rank 0 the gate columns [col0, +128), rank 1 the matching up columns [N + col0, +128)
+        const int bx = EPI == 1 ? (rank == 0 ? col0 : N + col0) : col0 + (int)rank * 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!tc::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t sa = smem_addr + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const uint32_t leader_full = tc::map_to_rank(full_bar(stage), 0);
+          if (rank == 0) tc::mbar_arrive_expect_tx(full_bar(stage), 2u * STAGE_BYTES);  // both CTAs' bytes
+          tc::tma_load_2d_pair(sa, &tmA, kb * BK, row0, leader_full);
+          tc::tma_load_2d_pair(sb, &tmB, bx, kb * BK, leader_full);
+          tc::tma_load_2d_pair(sb + BK * 128, &tmB, bx + 64, kb * BK, leader_full);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = tc::make_idesc_f16_f32(256, BN, 0, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int t = 0;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++t) {
+        const int acc = t & 1;
+        if (!tc::mbar_wait(tempty_bar(acc), ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag)) break;
+        tc::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!tc::mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          tc::tc_fence_after();
+          const uint32_t sa = smem_addr + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const uint64_t adesc = tc::make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bdesc = tc::make_smem_desc_sw128(sb, BK * 128, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            tc::mma_f16_ss_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), idesc,
+                                (kb | k) != 0 ? 1u : 0u);
+          tc::mma_commit_pair_mc(empty_bar(stage), 3);  // frees the stage in both CTAs
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc::mma_commit_pair_mc(tfull_bar(acc), 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int q = warp & 3;
+    int t = 0;
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++t) {
+      const int tm = tile % tiles_m, col_base = (tile / tiles_m) * OUT_COLS;
+      const int acc = t & 1;
+      if (!tc::mbar_wait(tfull_bar(acc), (uint32_t)(t >> 1) & 1u, abort_flag)) break;
+      tc::tc_fence_after();
+      const int row = tm * 256 + (int)rank * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+      OutT *crow = C + (int64_t)row * ldc;
+      const __half *rrow = R ? R + (int64_t)row * ldr : nullptr;
+      if constexpr (EPI == 1) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), g);
+          tc::tmem_ld_32x32(taddr + (uint32_t)(BN / 2 + c * 32), u);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float gv = __uint_as_float(g[e]);
+            g[e] = __float_as_uint((gv / (1.0f + __expf(-gv))) * __uint_as_float(u[e]));
+          }
+          const int col0 = col_base + c * 32;
+          if (row < M && col0 < N) store_row_chunk<OutT>(crow, nullptr, g, col0, N, vec_ok != 0);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
+          tc::tmem_ld_wait();
+          const int col0 = col_base + c * 32;
+          if (row < M && col0 < N) store_row_chunk<OutT>(crow, rrow, v, col0, N, vec_ok != 0);
+        }
+      }
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_rank(tempty_bar(acc), 0));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc::tc_fence_before();
+  tc::cluster_sync_all();  // nobody leaves while the peer may still signal or read this CTA
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_status, (int)HEXB_ERR_TIMEOUT);
+}
+
+template <typename OutT, int EPI>
+static int launch_tc_pair(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M, int N,
+                          int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count, cudaStream_t st) {
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = gemm_tc_pair_kernel<OutT, EPI>;
+  if (!attr_done[dev & 63]) {
+    HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES));
+    attr_done[dev & 63] = true;
+  }
+  constexpr int OUT_COLS = EPI == 1 ? pair::BN / 2 : pair::BN;
+  const int tiles_m = (M + 255) / 256, tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
+  const int tiles = tiles_m * tiles_n;
+  const int clusters = tiles < sm_count / 2 ? tiles : sm_count / 2;
+  kern<<<2 * clusters, THREADS, pair::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok);
+  return check_launch("gemm_tc_pair");
+}
+
 template <int BN, int STAGES, typename OutT, int EPI = 0>
 static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M,
                      int N, int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count,
@@ -379,6 +580,10 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
     if (N <= 64 || (int64_t)tiles_m * ((N + 127) / 128) < di.sm_count / 2) bn = 64;
     else if (N <= 128 || (int64_t)tiles_m * ((N + 255) / 256) < di.sm_count) bn = 128;
   }
+  // CTA-pair kernel for problems with at least one 256 x 256 tile per pair of SMs
+  const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  if (option("gemm_bn", 0) == 0 && option("gemm_pair", 1) && pair_tiles >= di.sm_count / 2)
+    return launch_tc_pair<OutT, 0>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
   switch (bn) {
     case 64:
       return launch_tc<64, 8, OutT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
@@ -443,6 +648,9 @@ extern "C" int hexb_matmul_swiglu_f16(const void *A, const void *B_gate_up, void
     if (int s = encode_tmap_f16_sw128(&tmB, B_gate_up, 2, dims, strides, box)) return s;
   }
   const int vec_ok = (ldo % 8 == 0) && aligned16(out);
+  if (option("gemm_pair", 1) && ((M + 255) / 256) * ((F + 127) / 128) >= di.sm_count / 2)
+    return launch_tc_pair<__half, 1>(tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
+                                     di.sm_count, (cudaStream_t)stream);
   return launch_tc<256, 4, __half, 1>(tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
                                       di.sm_count, (cudaStream_t)stream);
 }
