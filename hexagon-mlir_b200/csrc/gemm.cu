@@ -100,7 +100,9 @@ __device__ __forceinline__ void store_row_chunk<float>(float *crow, const __half
 // EPI == 1 (SwiGLU, BN = 256, fp16 out): B is a [K, 2*N] gate|up matrix; a tile's B operand is made
 // of 128 gate columns [col0, col0+128) and the 128 up columns [N+col0, N+col0+128), so accumulator
 // columns c and 128+c belong to output column col0+c and the epilogue writes silu(gate) * up.
-template <int BN, int STAGES, typename OutT, int EPI = 0>
+// BT: B is given transposed, Bt[N, K] row-major (C = A @ Bt^T): it is then the K-major operand form,
+// loaded as 128-row x 64-k boxes like A.
+template <int BN, int STAGES, typename OutT, int EPI = 0, bool BT = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
@@ -183,13 +185,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (!tc::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t sa = smem_addr + stage * cfg::STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
-          tc::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(A_BYTES + chunks * BK * 128));
+          tc::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(A_BYTES + (BT ? BN * 128 : chunks * BK * 128)));
           tc::tma_load_2d(sa, &tmA, kb * BK, w.tm * BM, full_bar(stage));
+          if constexpr (BT) {
+            // rows of Bt = output columns; boxes of 128 rows x 64 k (the whole BN is always loaded)
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j) {
-            int x = w.col0 + j * 64;
-            if (EPI == 1 && j >= BN / 128) x = N + w.col0 + (j - BN / 128) * 64;  // the matching up columns
-            if (j < chunks) tc::tma_load_2d(sb + j * (BK * 128), &tmB, x, kb * BK, full_bar(stage));
+            for (int j = 0; j < BN / 128; ++j) {
+              int n0 = w.col0 + j * 128;
+              if (EPI == 1 && j >= 1) n0 = N + w.col0;  // the matching up rows
+              tc::tma_load_2d(sb + j * (128 * 128), &tmB, kb * BK, n0, full_bar(stage));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) {
+              int x = w.col0 + j * 64;
+              if (EPI == 1 && j >= BN / 128) x = N + w.col0 + (j - BN / 128) * 64;  // the matching up columns
+              if (j < chunks) tc::tma_load_2d(sb + j * (BK * 128), &tmB, x, kb * BK, full_bar(stage));
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -203,7 +215,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = true;
       int t = 0;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++t) {
-        const uint32_t idesc = tc::make_idesc_f16_f32(BM, item_of(item).width, 0, 1);
+        const uint32_t idesc = tc::make_idesc_f16_f32(BM, item_of(item).width, 0, BT ? 0 : 1);
         const int acc = t & 1;
         if (!tc::mbar_wait(tempty_bar(acc), ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag)) break;
         tc::tc_fence_after();
@@ -214,11 +226,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sa = smem_addr + stage * cfg::STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
           const uint64_t adesc = tc::make_smem_desc_sw128(sa, 16, 1024);
-          const uint64_t bdesc = tc::make_smem_desc_sw128(sb, b_lbo, b_sbo);
+          const uint64_t bdesc = BT ? tc::make_smem_desc_sw128(sb, 16, 1024) : tc::make_smem_desc_sw128(sb, b_lbo, b_sbo);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            // A: +32 bytes inside the 128-byte swizzle row; B: +16 k-rows = 2 swizzle atoms.
-            tc::mma_f16_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), idesc,
+            // A (and a K-major B): +32 bytes inside the 128-byte swizzle row; N-major B: +16 k-rows = 2 atoms.
+            tc::mma_f16_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(BT ? k * 2 : k * 128), idesc,
                            (kb | k) != 0 ? 1u : 0u);
           }
           tc::mma_commit(empty_bar(stage));
@@ -291,14 +303,14 @@ template <typename OutT>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const __half *__restrict__ A, const __half *__restrict__ B, OutT *__restrict__ C,
                  const __half *__restrict__ R, int64_t M, int64_t N, int64_t K, int64_t lda,
-                 int64_t ldb, int64_t ldc, int64_t ldr) {
+                 int64_t ldb, int64_t ldc, int64_t ldr, int bt) {
   __shared__ float As[16][17], Bs[16][17];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int64_t row = (int64_t)blockIdx.y * 16 + ty, col = (int64_t)blockIdx.x * 16 + tx;
   float acc = 0.f;
   for (int64_t k0 = 0; k0 < K; k0 += 16) {
     As[ty][tx] = (row < M && k0 + tx < K) ? __half2float(A[row * lda + k0 + tx]) : 0.f;
-    Bs[ty][tx] = (k0 + ty < K && col < N) ? __half2float(B[(k0 + ty) * ldb + col]) : 0.f;
+    Bs[ty][tx] = (k0 + ty < K && col < N) ? __half2float(bt ? B[col * ldb + k0 + ty] : B[(k0 + ty) * ldb + col]) : 0.f;
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < 16; ++k) acc = fmaf(As[ty][k], Bs[k][tx], acc);
@@ -328,7 +340,7 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 10
 constexpr int TMEM_COLS = 512;
 }  // namespace pair
 
-template <typename OutT, int EPI>
+template <typename OutT, int EPI, bool BT = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
@@ -399,8 +411,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t leader_full = tc::map_to_rank(full_bar(stage), 0);
           if (rank == 0) tc::mbar_arrive_expect_tx(full_bar(stage), 2u * STAGE_BYTES);  // both CTAs' bytes
           tc::tma_load_2d_pair(sa, &tmA, kb * BK, row0, leader_full);
-          tc::tma_load_2d_pair(sb, &tmB, bx, kb * BK, leader_full);
-          tc::tma_load_2d_pair(sb + BK * 128, &tmB, bx + 64, kb * BK, leader_full);
+          if constexpr (BT) {
+            tc::tma_load_2d_pair(sb, &tmB, kb * BK, bx, leader_full);  // 128 rows of Bt x 64 k
+          } else {
+            tc::tma_load_2d_pair(sb, &tmB, bx, kb * BK, leader_full);
+            tc::tma_load_2d_pair(sb + BK * 128, &tmB, bx + 64, kb * BK, leader_full);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -408,7 +424,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = tc::make_idesc_f16_f32(256, BN, 0, 1);
+      constexpr uint32_t idesc = tc::make_idesc_f16_f32(256, BN, 0, BT ? 0 : 1);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -424,10 +440,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t sa = smem_addr + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
           const uint64_t adesc = tc::make_smem_desc_sw128(sa, 16, 1024);
-          const uint64_t bdesc = tc::make_smem_desc_sw128(sb, BK * 128, 1024);
+          const uint64_t bdesc = BT ? tc::make_smem_desc_sw128(sb, 16, 1024) : tc::make_smem_desc_sw128(sb, BK * 128, 1024);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
-            tc::mma_f16_ss_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), idesc,
+            tc::mma_f16_ss_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(BT ? k * 2 : k * 128), idesc,
                                 (kb | k) != 0 ? 1u : 0u);
           tc::mma_commit_pair_mc(empty_bar(stage), 3);  // frees the stage in both CTAs
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -492,13 +508,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_status, (int)HEXB_ERR_TIMEOUT);
 }
 
-template <typename OutT, int EPI>
+template <typename OutT, int EPI, bool BT = false>
 static int launch_tc_pair(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M, int N,
                           int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count, cudaStream_t st) {
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = gemm_tc_pair_kernel<OutT, EPI>;
+  auto kern = gemm_tc_pair_kernel<OutT, EPI, BT>;
   if (!attr_done[dev & 63]) {
     HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES));
     attr_done[dev & 63] = true;
@@ -511,7 +527,7 @@ static int launch_tc_pair(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *
   return check_launch("gemm_tc_pair");
 }
 
-template <int BN, int STAGES, typename OutT, int EPI = 0>
+template <int BN, int STAGES, typename OutT, int EPI = 0, bool BT = false>
 static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M,
                      int N, int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count,
                      cudaStream_t st) {
@@ -519,7 +535,7 @@ static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, co
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = gemm_tc_kernel<BN, STAGES, OutT, EPI>;
+  auto kern = gemm_tc_kernel<BN, STAGES, OutT, EPI, BT>;
   if (!attr_done[dev & 63]) {
     HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
     attr_done[dev & 63] = true;
@@ -530,7 +546,7 @@ static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, co
   // split the tiles of the last partial wave into column slices (>= 64 wide) while they still fit one wave
   int full_items = tiles / sm_count * sm_count, split = 1;
   const int rem = tiles - full_items;
-  if (EPI == 0 && rem > 0 && option("gemm_tail_split", 1)) {
+  if (EPI == 0 && !BT && rem > 0 && option("gemm_tail_split", 1)) {
     while (split * 2 <= BN / 64 && rem * split * 2 <= sm_count) split *= 2;
   }
   if (split == 1) full_items = tiles;
@@ -543,7 +559,7 @@ static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, co
   return check_launch("gemm_tc");
 }
 
-template <typename OutT>
+template <typename OutT, bool BT = false>
 static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *R, int64_t M, int64_t N,
                        int64_t K, int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t st) {
   DeviceInfo di;
@@ -555,7 +571,7 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
   if (!tc_ok) {
     dim3 grid((unsigned)((N + 15) / 16), (unsigned)((M + 15) / 16));
     if (grid.y > 65535) return HEXB_ERR_UNSUPPORTED;
-    gemm_simt_kernel<OutT><<<grid, 256, 0, st>>>(A, B, C, R, M, N, K, lda, ldb, ldc, ldr);
+    gemm_simt_kernel<OutT><<<grid, 256, 0, st>>>(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, BT ? 1 : 0);
     return check_launch("gemm_simt");
   }
   CUtensorMap tmA, tmB;
@@ -565,7 +581,12 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
     const uint32_t box[2] = {BK, BM};
     if (int s = encode_tmap_f16_sw128(&tmA, A, 2, dims, strides, box)) return s;
   }
-  {
+  if constexpr (BT) {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    const uint64_t strides[1] = {(uint64_t)ldb * 2};
+    const uint32_t box[2] = {BK, 128};
+    if (int s = encode_tmap_f16_sw128(&tmB, B, 2, dims, strides, box)) return s;
+  } else {
     const uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
     const uint64_t strides[1] = {(uint64_t)ldb * 2};
     const uint32_t box[2] = {64, BK};
@@ -583,14 +604,15 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
   // CTA-pair kernel for problems with at least one 256 x 256 tile per pair of SMs
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
   if (option("gemm_bn", 0) == 0 && option("gemm_pair", 1) && pair_tiles >= di.sm_count / 2)
-    return launch_tc_pair<OutT, 0>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+    return launch_tc_pair<OutT, 0, BT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+  if (BT && bn == 64) bn = 128;  // the transposed form loads Bt in 128-row boxes
   switch (bn) {
     case 64:
-      return launch_tc<64, 8, OutT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<64, 8, OutT, 0, false>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
     case 128:
-      return launch_tc<128, 6, OutT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<128, 6, OutT, 0, BT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
     default:
-      return launch_tc<256, 4, OutT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<256, 4, OutT, 0, BT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
   }
 }
 
@@ -620,6 +642,22 @@ extern "C" int hexb_matmul_f16(const void *A, const void *B, void *C, const void
                                      (const __half *)residual, M, N, K, lda, ldb, ldc, (cudaStream_t)stream);
   return gemm::matmul_impl<float>((const __half *)A, (const __half *)B, (float *)C,
                                   (const __half *)residual, M, N, K, lda, ldb, ldc, (cudaStream_t)stream);
+}
+
+extern "C" int hexb_matmul_f16_nt(const void *A, const void *Bt, void *C, const void *residual, int64_t M,
+                                  int64_t N, int64_t K, int64_t lda, int64_t ldbt, int64_t ldc, int out_dtype,
+                                  void *stream) {
+  using namespace hexb;
+  if (M < 0 || N < 0 || K < 0) return HEXB_ERR_BAD_ARG;
+  if (out_dtype != HEXB_DT_F16 && out_dtype != HEXB_DT_F32) return HEXB_ERR_UNSUPPORTED;
+  if (M == 0 || N == 0) return HEXB_OK;
+  if (!C || (K > 0 && (!A || !Bt))) return HEXB_ERR_BAD_ARG;
+  if (lda < K || ldbt < K || ldc < N) return HEXB_ERR_BAD_ARG;
+  if (out_dtype == HEXB_DT_F16)
+    return gemm::matmul_impl<__half, true>((const __half *)A, (const __half *)Bt, (__half *)C,
+                                           (const __half *)residual, M, N, K, lda, ldbt, ldc, (cudaStream_t)stream);
+  return gemm::matmul_impl<float, true>((const __half *)A, (const __half *)Bt, (float *)C, (const __half *)residual,
+                                        M, N, K, lda, ldbt, ldc, (cudaStream_t)stream);
 }
 
 extern "C" int hexb_matmul_swiglu_f16(const void *A, const void *B_gate_up, void *out, int64_t M, int64_t F,

@@ -159,6 +159,26 @@ def matmul(a, b, c, residual=None) -> None:
         check(lib.hexb_matmul_f16_host(_ptr(a), _ptr(b), _ptr(c), M, N, K, _dt(c)), "matmul_host")
 
 
+def matmul_nt(a, bt, c, residual=None) -> None:
+    """c = a @ bt.T for a [M, K], bt [N, K] (a weight stored transposed), float16 CUDA tensors; c float16 or
+    float32.  Reference: test/python/torch-mlir/test_hexkl_macro_matmul.py:24-28,51-69."""
+    lib = _lib.load()
+    _same_place(a, bt, c, residual)
+    if a.dtype != torch.float16 or bt.dtype != torch.float16:
+        raise TypeError("matmul_nt: A and Bt must be float16")
+    M, K, lda = _rows2d(a, "A")
+    N, K2, ldb = _rows2d(bt, "Bt")
+    M2, N2, ldc = _rows2d(c, "C")
+    if K != K2 or M != M2 or N != N2:
+        raise ValueError("matmul_nt: shapes do not agree")
+    if residual is not None and (residual.dtype != torch.float16 or residual.shape != c.shape
+                                 or residual.stride(0) != c.stride(0)):
+        raise ValueError("matmul_nt: residual must be float16 with C's shape and leading dimension")
+    with torch.cuda.device(a.device):
+        check(lib.hexb_matmul_f16_nt(_ptr(a), _ptr(bt), _ptr(c), _ptr(residual), M, N, K, lda, ldb, ldc, _dt(c),
+                                     _stream(a)), "matmul_nt")
+
+
 def matmul_swiglu(a, b_gate_up, out) -> None:
     """out = silu(a @ b[:, :F]) * (a @ b[:, F:]) for a [M, K], b [K, 2F], out [M, F]; float16 CUDA tensors."""
     lib = _lib.load()

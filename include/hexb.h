@@ -88,6 +88,14 @@ int hexb_matmul_f16(const void *A, const void *B, void *C, const void *residual,
                     int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int out_dtype,
                     void *stream);
 
+/* The same product with the weight given transposed: C[M,N] = A[M,K] @ Bt[N,K]^T (Bt row-major with
+ * leading dimension ldbt).  Replaces: the `matmul(x, weight.T)` form of the HexKL macro test
+ * (test/python/torch-mlir/test_hexkl_macro_matmul.py:24-28,51-69) and the transpose folding of
+ * qcom_hexagon_backend/lib/Transforms/ScheduleMatmulForHVXPass.cpp. */
+int hexb_matmul_f16_nt(const void *A, const void *Bt, void *C, const void *residual, int64_t M,
+                       int64_t N, int64_t K, int64_t lda, int64_t ldbt, int64_t ldc, int out_dtype,
+                       void *stream);
+
 /* Gate/up projection with the SwiGLU gating fused into the epilogue:
  *   out[M, F] = silu(A @ B[:, 0:F]) * (A @ B[:, F:2F]),  B = [K, 2F] row-major (columns gate|up).
  * fp32 accumulation and gating, one rounding to fp16.  Composed from matmul

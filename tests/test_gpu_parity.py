@@ -500,3 +500,26 @@ def test_decoder_fused_and_unfused_gating_agree(dev):
     assert O.max_rel_err(outs[0], outs[1]) < 5e-3
     ref = O.torch_decoder(x, ws, H, d // H, f, B, S, 1e-6)
     assert O.max_rel_err(outs[0], ref) < REL_F16 and O.max_rel_err(outs[1], ref) < REL_F16
+
+
+# ------------------------------------------------------------------ matmul with the weight stored transposed
+@pytest.mark.parametrize("M,N,K", [(1024, 256, 512),          # the reference's transposed case
+                                   (128, 128, 64), (256, 512, 128), (100, 72, 40), (129, 264, 136),
+                                   (37, 29, 13), (4096, 4096, 1024), (2560, 2560, 256)])
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+def test_matmul_nt_vs_oracle(dev, M, N, K, out_dtype):
+    g = torch.Generator().manual_seed(M * 3 + N * 5 + K)
+    a = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(N, K, generator=g) * K ** -0.5).half()           # weight [N, K]; the product uses w.T
+    c = torch.empty(M, N, dtype=out_dtype, device=dev)
+    ops.matmul_nt(a.to(dev), w.to(dev), c)
+    torch.cuda.synchronize()
+    assert hexb200.device_status() == 0
+    ref = torch.matmul(a.float(), w.float().T)
+    assert O.max_rel_err(c.cpu(), ref) < (REL_F16 if out_dtype == torch.float16 else REL_F32)
+    if out_dtype == torch.float16:
+        assert torch.allclose(c.cpu().float(), ref, rtol=1e-2, atol=1e-2)   # the reference test's tolerance
+    # same numbers as the non-transposed entry point on a materialised w.T
+    c2 = torch.empty(M, N, dtype=out_dtype, device=dev)
+    ops.matmul(a.to(dev), w.T.contiguous().to(dev), c2)
+    assert O.max_rel_err(c.cpu(), c2.cpu()) < 1e-3
