@@ -37,6 +37,17 @@ class DecoderWeights(C.Structure):
     _fields_ = [(n, C.POINTER(C.c_void_p)) for n in ("wqkv", "wo", "wgu", "wd", "g1", "g2")]
 
 
+class AttentionDesc(C.Structure):
+    """hexb_attention_desc of include/hexb.h."""
+    _fields_ = [
+        ("Q", C.c_void_p), ("K", C.c_void_p), ("V", C.c_void_p), ("Out", C.c_void_p), ("mask", C.c_void_p),
+        ("Z", C.c_int64), ("H", C.c_int64), ("N_Q", C.c_int64), ("N_KV", C.c_int64), ("D", C.c_int64),
+        ("strides", C.c_int64 * 12), ("mask_strides", C.c_int64 * 3),
+        ("in_dtype", C.c_int), ("out_dtype", C.c_int), ("mask_dtype", C.c_int),
+        ("sm_scale", C.c_float), ("causal", C.c_int),
+    ]
+
+
 _i64, _vp, _f, _i = C.c_int64, C.c_void_p, C.c_float, C.c_int
 
 # name -> (restype, argtypes); mirrors include/hexb.h one to one.
@@ -55,6 +66,7 @@ PROTOTYPES = {
     "hexb_matmul_f16_nt": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i, _vp]),
     "hexb_matmul_swiglu_f16": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
     "hexkl_matmul_f16f16_f32": (_i, [_i64, _i64, _i64, _vp, _vp, _vp]),
+    "hexb_attention_fwd_ex": (_i, [C.POINTER(AttentionDesc), _vp]),
     "hexb_attention_fwd_f16": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, C.POINTER(_i64), _f, _i, _vp]),
     "hexb_attention_fwd_f32": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, C.POINTER(_i64), _f, _i, _vp]),
     "hexb_silu_f32": (_i, [_vp, _vp, _i64, _vp]),

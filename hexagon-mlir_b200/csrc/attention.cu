@@ -98,9 +98,17 @@ struct Params {
 #ifdef HEXB_ATTN_PROFILE
   unsigned long long *prof;
 #endif
-  __half *out;
+  void *out;           // __half, or float when out_f32
   int64_t so_z, so_h, so_n;
-  int Z, H, N_CTX;
+  int Z, H, N_CTX;     // N_CTX: query rows
+  int N_KV;            // key/value rows (the 128-key kernel takes N_KV == N_CTX only)
+  int out_f32;
+  const void *mask;    // additive mask [Z, H, N_CTX, N_KV] (strides below, innermost 1), or null
+  int mask_f32;        // mask element type: 1 float, 0 __half
+  int mask_vec_ok;     // 16-byte loads of the mask row are aligned
+  int mask_tma;        // the mask arrives through the tensor map (fp16, 16-byte aligned strides, one row per query)
+  int mask_h_on, mask_z_on;   // 0: that dimension of the mask is broadcast (its tensor-map extent is 1)
+  int64_t sm_z, sm_h, sm_q;
   int num_q_tiles;
   int tiles_per_cta;   // query tiles one CTA walks (1 or 2)
   int ctas_per_bh;     // num_q_tiles / tiles_per_cta
@@ -327,7 +335,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!ok || !tc::mbar_wait(o_full, (uint32_t)t & 1u, abort_flag)) { ok = false; break; }
       tc::tc_fence_after();
       const float inv = 1.0f / l;
-      __half *orow = p.out + (int64_t)z * p.so_z + (int64_t)h * p.so_h + (int64_t)qi * p.so_n;
+      __half *orow = static_cast<__half *>(p.out) + (int64_t)z * p.so_z + (int64_t)h * p.so_h + (int64_t)qi * p.so_n;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t o[32];
@@ -390,27 +398,44 @@ struct Cfg2 {
   static constexpr int Q_CHUNK = 128 * 128;           // 128 rows x 128 bytes
   static constexpr int KV_BYTES = BN * HD * 2;
   static constexpr int KV_CHUNK = BN * 128;           // 64 rows x 128 bytes
-  static constexpr int NBAR = 17;
+  static constexpr int NBAR = 21;
   static constexpr int NEEDED = Q_BYTES + 4 * KV_BYTES + NBAR * 8 + 16 + 1024;
   static constexpr int SMEM_BYTES = NEEDED < 100 * 1024 ? 100 * 1024 : NEEDED;  // caps residency at 2 CTAs/SM
+  // Masked variant: one 32-row x 64-key fp16 mask tile per softmax warp, filled by TMA.  Two CTAs of
+  // this size still fit one SM only if the 1024-byte alignment of the buffers costs no padding, which
+  // the declared alignment of the dynamic shared array provides; the kernel checks it and reports
+  // a status instead of running past its allocation if that ever fails to hold.
+  static constexpr int MASK_STAGE = 32 * 128;
+  static constexpr int MASK_BYTES = 4 * MASK_STAGE;
+  static constexpr int SMEM_BYTES_MASK = Q_BYTES + 4 * KV_BYTES + MASK_BYTES + NBAR * 8 + 16 + 160;
   static constexpr int TMEM_COLS = 256;               // S0 [0,64), S1 [64,128), O [128,128+HD); P_b over S_b[0,32)
   static constexpr int O_COL = 128;
 };
 
-template <int HD>
+// MASK: an additive mask tile is read by the softmax warps and the scores are formed in the base-2
+// domain as s * scale * log2(e) + mask * log2(e) before the running maximum is taken.
+template <int HD, bool MASK>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const Params p) {
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmM,
+                    const Params p) {
   using cfg = Cfg2<HD>;
   constexpr int BN = cfg::BN;
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+  constexpr uint32_t kMaskBytes = MASK ? cfg::MASK_BYTES : 0;
+  if (MASK && pad + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + cfg::NBAR * 8 + 16 > (uint32_t)cfg::SMEM_BYTES_MASK) {
+    // the layout would not fit the allocation: every thread leaves before any barrier or TMEM use
+    if (threadIdx.x == 0) atomicExch(&g_attn_status, (int)HEXB_ERR_MISALIGNED);
+    return;
+  }
   uint8_t *smem = smem_raw + pad;
   const uint32_t smem_addr = raw_addr + pad;
   const uint32_t sQ = smem_addr;
   const uint32_t sK0 = sQ + cfg::Q_BYTES, sV0 = sK0 + 2 * cfg::KV_BYTES;
-  const uint32_t bar0 = sV0 + 2 * cfg::KV_BYTES;
+  const uint32_t sM0 = sV0 + 2 * cfg::KV_BYTES;   // mask tiles (masked variant only)
+  const uint32_t bar0 = sM0 + kMaskBytes;
   const uint32_t q_full = bar0, q_empty = bar0 + 8, o_full = bar0 + 16, o_empty = bar0 + 24, pv_done = bar0 + 32;
   auto k_full = [&](uint32_t b) { return bar0 + 40 + 8 * b; };
   auto k_empty = [&](uint32_t b) { return bar0 + 56 + 8 * b; };
@@ -419,7 +444,8 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   auto s_full = [&](uint32_t b) { return bar0 + 104 + 8 * b; };
   // p_full[2] follow at +120 (NBAR = 15 counts q_full..s_full; two more for p_full)
   auto p_full = [&](uint32_t b) { return bar0 + 120 + 8 * b; };
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + cfg::Q_BYTES + 4 * cfg::KV_BYTES + 136);
+  auto m_full = [&](uint32_t w) { return bar0 + 136 + 8 * w; };   // one per softmax warp
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + 168);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -427,7 +453,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int bh = blockIdx.x / p.ctas_per_bh;
   const int q_rank = blockIdx.x - bh * p.ctas_per_bh;
   const int z = bh / p.H, h = bh - z * p.H;
-  const int kv_blocks = (p.N_CTX + BN - 1) / BN;
+  const int kv_blocks = (p.N_KV + BN - 1) / BN;
   auto tile_of = [&](int t) {
     if (p.causal) return t == 0 ? p.num_q_tiles - 1 - q_rank : q_rank;
     return q_rank * p.tiles_per_cta + t;
@@ -452,11 +478,13 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc::mbar_init(s_full(b), 1);
       tc::mbar_init(p_full(b), 4);
     }
+    for (uint32_t w = 0; w < 4; ++w) tc::mbar_init(m_full(w), 1);
     *abort_flag = 0;
     tc::fence_barrier_init();
     tc::prefetch_tensormap(&tmQ);
     tc::prefetch_tensormap(&tmK);
     tc::prefetch_tensormap(&tmV);
+    if (MASK && p.mask_tma) tc::prefetch_tensormap(&tmM);
   }
   if (warp == 1) {
     tc::tmem_alloc(tc::smem_u32(tmem_slot), cfg::TMEM_COLS);
@@ -561,6 +589,18 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     uint32_t it = 0;
     bool ok = true;
+    // Mask tiles by TMA: this warp's 32 rows x 64 keys land in its own staging buffer (128-byte
+    // swizzle); the copy of the next block's tile is issued as soon as the current one is in registers.
+    const uint32_t sM = sM0 + (uint32_t)q * cfg::MASK_STAGE;
+    const uint32_t mbar = m_full((uint32_t)q);
+    uint32_t mit = 0;
+    auto issue_mask = [&](int q_tile, int j) {
+      if (lane == 0) {
+        tc::mbar_arrive_expect_tx(mbar, cfg::MASK_STAGE);
+        tc::tma_load_4d(sM, &tmM, j * BN, q_tile * BLOCK_M + q * 32, p.mask_h_on ? h : 0, p.mask_z_on ? z : 0, mbar);
+      }
+    };
+    if (MASK && p.mask_tma) issue_mask(tile_of(0), 0);
     HEXB_PROF_DECL(8)
     for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
       const int q_tile = tile_of(t);
@@ -568,6 +608,10 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int m0 = q_tile * BLOCK_M;
       const int qi = m0 + r;
       float m_ref = -INFINITY, l = 0.f;
+      const int64_t mrow_off = (int64_t)z * p.sm_z + (int64_t)h * p.sm_h + (int64_t)qi * p.sm_q;
+      const float *mrow_f32 = static_cast<const float *>(p.mask) + mrow_off;
+      const __half *mrow_f16 = static_cast<const __half *>(p.mask) + mrow_off;
+      (void)mrow_f32; (void)mrow_f16;
       for (int j = 0; j < n_kv; ++j, ++it) {
         const uint32_t b = it & 1u, ph = (it >> 1) & 1u;
         HEXB_PROF(0)  // loop / epilogue of the previous tile
@@ -576,18 +620,84 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc::tc_fence_after();
         const uint32_t tS = tmem_base + b * BN, tP = tS;
         const int kv0 = j * BN;
-        const bool need_mask = (p.causal && kv0 + BN - 1 > m0) || (kv0 + BN > p.N_CTX);
+        const bool need_mask = (p.causal && kv0 + BN - 1 > m0) || (kv0 + BN > p.N_KV);
         uint32_t sv[BN];
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c)
           tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c * 32), reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
         tc::tmem_ld_wait();
         HEXB_PROF(2)  // TMEM load of S
+        if constexpr (MASK) {
+          // sv <- s * scale_log2 + mask * log2(e); rows past the end read no mask
+          constexpr float kLog2e = 1.44269504f;
+          const bool row_ok = qi < p.N_CTX;
+          if (p.mask_tma) {
+            if (!tc::mbar_wait(mbar, mit & 1u, abort_flag)) { ok = false; break; }
+            ++mit;
+            const uint8_t *mrow_s = smem + (sM - smem_addr) + lane * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              Vec16<__half> mv;
+              mv.raw = *reinterpret_cast<const uint4 *>(mrow_s + ((c ^ (lane & 7)) << 4));
+              float mf[8];
+              mv.unpack(mf);
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                sv[c * 8 + u] = __float_as_uint(fmaf(__uint_as_float(sv[c * 8 + u]), p.scale_log2, mf[u] * kLog2e));
+            }
+            __syncwarp();  // every lane has read the tile: the buffer may be refilled
+            if (j + 1 < n_kv) issue_mask(q_tile, j + 1);
+            else if (t + 1 < p.tiles_per_cta) issue_mask(tile_of(t + 1), 0);
+          } else if (p.mask_f32) {
+            const float *mp = mrow_f32 + kv0;
+            if (j + 1 < n_kv && row_ok) {  // the next block of this row starts inside the row
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(mp + BN));
+              if (kv0 + BN + 32 < p.N_KV) asm volatile("prefetch.global.L2 [%0];" ::"l"(mp + BN + 32));
+            }
+            if (row_ok && p.mask_vec_ok && kv0 + BN <= p.N_KV) {
+#pragma unroll
+              for (int e = 0; e < BN; e += 4) {
+                const float4 mv = __ldg(reinterpret_cast<const float4 *>(mp + e));
+                sv[e + 0] = __float_as_uint(fmaf(__uint_as_float(sv[e + 0]), p.scale_log2, mv.x * kLog2e));
+                sv[e + 1] = __float_as_uint(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, mv.y * kLog2e));
+                sv[e + 2] = __float_as_uint(fmaf(__uint_as_float(sv[e + 2]), p.scale_log2, mv.z * kLog2e));
+                sv[e + 3] = __float_as_uint(fmaf(__uint_as_float(sv[e + 3]), p.scale_log2, mv.w * kLog2e));
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < BN; ++e) {
+                const float mv = (row_ok && kv0 + e < p.N_KV) ? __ldg(mp + e) : 0.f;
+                sv[e] = __float_as_uint(fmaf(__uint_as_float(sv[e]), p.scale_log2, mv * kLog2e));
+              }
+            }
+          } else {
+            const __half *mp = mrow_f16 + kv0;
+            if (j + 1 < n_kv && row_ok) asm volatile("prefetch.global.L2 [%0];" ::"l"(mp + BN));
+            if (row_ok && p.mask_vec_ok && kv0 + BN <= p.N_KV) {
+#pragma unroll
+              for (int e = 0; e < BN; e += 8) {
+                Vec16<__half> mv;
+                mv.raw = __ldg(reinterpret_cast<const uint4 *>(mp + e));
+                float mf[8];
+                mv.unpack(mf);
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                  sv[e + u] = __float_as_uint(fmaf(__uint_as_float(sv[e + u]), p.scale_log2, mf[u] * kLog2e));
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < BN; ++e) {
+                const float mv = (row_ok && kv0 + e < p.N_KV) ? __half2float(__ldg(mp + e)) : 0.f;
+                sv[e] = __float_as_uint(fmaf(__uint_as_float(sv[e]), p.scale_log2, mv * kLog2e));
+              }
+            }
+          }
+        }
         if (need_mask) {
 #pragma unroll
           for (int e = 0; e < BN; ++e) {
             const int kv = kv0 + e;
-            if ((p.causal && kv > qi) || kv >= p.N_CTX) sv[e] = 0xff800000u;
+            if ((p.causal && kv > qi) || kv >= p.N_KV) sv[e] = 0xff800000u;
           }
         }
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -597,7 +707,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int u = 0; u < 4; ++u)
             mx4[u] = max3(mx4[u], __uint_as_float(sv[e + 2 * u]), __uint_as_float(sv[e + 2 * u + 1]));
         }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * (MASK ? 1.0f : p.scale_log2);
         const float m_new = fmaxf(m_ref, mx);
         if (j == 0) {
           m_ref = m_new;
@@ -619,15 +729,17 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
         HEXB_PROF(3)  // mask, max, rescale
-        const float neg_m = -m_ref;
+        // a row whose keys so far are all masked to -inf keeps m_ref = -inf: its weights must come out 0, not NaN
+        const float neg_m = (MASK && m_ref == -INFINITY) ? 0.f : -m_ref;
+        const float mul = MASK ? 1.0f : p.scale_log2;
         float l0 = 0.f, l1 = 0.f;
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + e]), p.scale_log2, neg_m));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + e + 1]), p.scale_log2, neg_m));
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + e]), mul, neg_m));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + e + 1]), mul, neg_m));
             l0 += p0;
             l1 += p1;
             pk[e >> 1] = pack_f16x2(p0, p1);
@@ -645,7 +757,9 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (!ok || !tc::mbar_wait(o_full, (uint32_t)t & 1u, abort_flag)) { ok = false; break; }
       tc::tc_fence_after();
       const float inv = 1.0f / l;
-      __half *orow = p.out + (int64_t)z * p.so_z + (int64_t)h * p.so_h + (int64_t)qi * p.so_n;
+      const int64_t orow_off = (int64_t)z * p.so_z + (int64_t)h * p.so_h + (int64_t)qi * p.so_n;
+      __half *orow = static_cast<__half *>(p.out) + orow_off;
+      float *orow32 = static_cast<float *>(p.out) + orow_off;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t o[32];
@@ -656,7 +770,19 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(o_empty);
         }
-        if (qi < p.N_CTX) {
+        if (qi < p.N_CTX && p.out_f32) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 f = make_float4(__uint_as_float(o[g * 4]) * inv, __uint_as_float(o[g * 4 + 1]) * inv,
+                                   __uint_as_float(o[g * 4 + 2]) * inv, __uint_as_float(o[g * 4 + 3]) * inv);
+            if (p.out_vec_ok) {
+              *reinterpret_cast<float4 *>(orow32 + c * 32 + g * 4) = f;
+            } else {
+              orow32[c * 32 + g * 4] = f.x; orow32[c * 32 + g * 4 + 1] = f.y;
+              orow32[c * 32 + g * 4 + 2] = f.z; orow32[c * 32 + g * 4 + 3] = f.w;
+            }
+          }
+        } else if (qi < p.N_CTX) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             float f[8];
@@ -705,7 +831,8 @@ attn_fwd_simt_kernel(const T *__restrict__ Q, const T *__restrict__ K, const T *
                      const int64_t sq_h, const int64_t sq_n, const int64_t sk_z, const int64_t sk_h,
                      const int64_t sk_n, const int64_t sv_z, const int64_t sv_h, const int64_t sv_n,
                      const int64_t so_z, const int64_t so_h, const int64_t so_n, float scale_log2,
-                     int causal) {
+                     int causal, int N_KV, int out_f32, const void *__restrict__ mask, int mask_f32,
+                     const int64_t sm_z, const int64_t sm_h, const int64_t sm_q) {
   constexpr int DPL = MAXD / 32;  // output columns per lane
   __shared__ float qs[4][MAXD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -724,7 +851,8 @@ attn_fwd_simt_kernel(const T *__restrict__ Q, const T *__restrict__ K, const T *
 #pragma unroll
   for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
   float m = -INFINITY, l = 0.f;
-  const int kv_end = causal ? qi + 1 : N_CTX;
+  const int kv_end = (causal && qi + 1 < N_KV) ? qi + 1 : N_KV;
+  const int64_t mrow = z * sm_z + h * sm_h + (int64_t)qi * sm_q;
   for (int kv0 = 0; kv0 < kv_end; kv0 += 32) {
     const int kv = kv0 + lane;
     float s = -INFINITY;
@@ -733,12 +861,18 @@ attn_fwd_simt_kernel(const T *__restrict__ Q, const T *__restrict__ K, const T *
       float dot = 0.f;
       for (int d = 0; d < D; ++d) dot = fmaf(qs[warp][d], to_f32<T>(kr[d]), dot);
       s = dot * scale_log2;
+      if (mask) {
+        const float mv = mask_f32 ? static_cast<const float *>(mask)[mrow + kv]
+                                  : __half2float(static_cast<const __half *>(mask)[mrow + kv]);
+        s = fmaf(mv, 1.44269504f, s);
+      }
     }
-    const float m_new = fmaxf(m, warp_max(s));
+    const float m_raw = fmaxf(m, warp_max(s));
+    const float m_new = m_raw == -INFINITY ? 0.f : m_raw;  // every key so far masked out: weights 0, not NaN
     const float pe = (kv < kv_end) ? exp2f(s - m_new) : 0.f;
     const float alpha = exp2f(m - m_new);  // m == -inf on the first step: alpha = 0, acc and l are 0
     l = l * alpha + warp_sum(pe);
-    m = m_new;
+    m = m_raw;
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] *= alpha;
     const int nvalid = kv_end - kv0 < 32 ? kv_end - kv0 : 32;
@@ -752,43 +886,59 @@ attn_fwd_simt_kernel(const T *__restrict__ Q, const T *__restrict__ K, const T *
       }
     }
   }
-  T *op = O + z * so_z + h * so_h + (int64_t)qi * so_n;
+  const int64_t ooff = z * so_z + h * so_h + (int64_t)qi * so_n;
   const float inv = 1.0f / l;
 #pragma unroll
   for (int i = 0; i < DPL; ++i) {
     const int d = lane + i * 32;
-    if (d < D) op[d] = from_f32<T>(acc[i] * inv);
+    if (d < D) {
+      if (out_f32) reinterpret_cast<float *>(O)[ooff + d] = acc[i] * inv;
+      else O[ooff + d] = from_f32<T>(acc[i] * inv);
+    }
   }
 }
 
+// Optional parts of a forward call: key length, output type, additive mask.
+struct Extra {
+  int64_t n_kv;
+  int out_f32;
+  const void *mask;
+  int mask_f32;
+  int64_t sm[3];
+};
+
 template <typename T>
-static int launch_simt(const T *Q, const T *K, const T *V, T *O, int64_t Z, int64_t H, int64_t N,
-                       int64_t D, const int64_t *s, float scale_log2, int causal, cudaStream_t st) {
+static int launch_simt(const T *Q, const T *K, const T *V, void *O, int64_t Z, int64_t H, int64_t N,
+                       int64_t D, const int64_t *s, float scale_log2, int causal, const Extra &x,
+                       cudaStream_t st) {
   if (D > 256) return HEXB_ERR_UNSUPPORTED;
   const int64_t rows = Z * H * N;
   const int64_t ctas = (rows + 3) / 4;
   if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
-  if (D <= 64)
-    attn_fwd_simt_kernel<T, 64><<<(unsigned)ctas, 128, 0, st>>>(Q, K, V, O, (int)Z, (int)H, (int)N, (int)D,
-        s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7], s[8], s[9], s[10], s[11], scale_log2, causal);
-  else if (D <= 128)
-    attn_fwd_simt_kernel<T, 128><<<(unsigned)ctas, 128, 0, st>>>(Q, K, V, O, (int)Z, (int)H, (int)N, (int)D,
-        s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7], s[8], s[9], s[10], s[11], scale_log2, causal);
-  else
-    attn_fwd_simt_kernel<T, 256><<<(unsigned)ctas, 128, 0, st>>>(Q, K, V, O, (int)Z, (int)H, (int)N, (int)D,
-        s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7], s[8], s[9], s[10], s[11], scale_log2, causal);
+  const int of32 = (sizeof(T) == 4) ? 1 : x.out_f32;
+#define HEXB_SIMT_LAUNCH(MAXD)                                                                              \
+  attn_fwd_simt_kernel<T, MAXD><<<(unsigned)ctas, 128, 0, st>>>(                                            \
+      Q, K, V, static_cast<T *>(O), (int)Z, (int)H, (int)N, (int)D, s[0], s[1], s[2], s[3], s[4], s[5], s[6], \
+      s[7], s[8], s[9], s[10], s[11], scale_log2, causal, (int)x.n_kv, of32, x.mask, x.mask_f32, x.sm[0],    \
+      x.sm[1], x.sm[2])
+  if (D <= 64) HEXB_SIMT_LAUNCH(64);
+  else if (D <= 128) HEXB_SIMT_LAUNCH(128);
+  else HEXB_SIMT_LAUNCH(256);
+#undef HEXB_SIMT_LAUNCH
   return check_launch("attn_simt");
 }
 
 template <int HD>
-static int launch_tc(const __half *Q, const __half *K, const __half *V, __half *O, int64_t Z, int64_t H,
-                     int64_t N, const int64_t *s, float scale_log2, int causal, cudaStream_t st) {
+static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O, int64_t Z, int64_t H,
+                     int64_t N, const int64_t *s, float scale_log2, int causal, const Extra &x, cudaStream_t st) {
   using cfg = Cfg<HD>;
-  const bool two_buffers = option("attn_kernel", 2) == 2;  // 2: 64-key blocks, two score buffers; 1: 128-key blocks
-  CUtensorMap tm[3];
+  // 2: 64-key blocks, two score buffers; 1: 128-key blocks (plain calls only)
+  const bool plain = !x.mask && !x.out_f32 && x.n_kv == N;
+  const bool two_buffers = !plain || option("attn_kernel", 2) == 2;
+  CUtensorMap tm[4];
   const __half *base[3] = {Q, K, V};
   for (int i = 0; i < 3; ++i) {
-    const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)N, (uint64_t)H, (uint64_t)Z};
+    const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)(i == 0 ? N : x.n_kv), (uint64_t)H, (uint64_t)Z};
     const uint64_t strides[3] = {(uint64_t)s[3 * i + 2] * 2, (uint64_t)s[3 * i + 1] * 2,
                                  (uint64_t)s[3 * i + 0] * 2};
     const uint32_t box[4] = {64, (i > 0 && two_buffers) ? 64u : 128u, 1, 1};
@@ -799,8 +949,10 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, __half *
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
     HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
-    HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg2<HD>::SMEM_BYTES));
+    HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg2<HD>::SMEM_BYTES_MASK));
     attr_done[dev & 63] = true;
   }
   Params p;
@@ -810,10 +962,39 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, __half *
   p.out = O;
   p.so_z = s[9]; p.so_h = s[10]; p.so_n = s[11];
   p.Z = (int)Z; p.H = (int)H; p.N_CTX = (int)N;
+  p.N_KV = (int)x.n_kv;
+  p.out_f32 = x.out_f32;
+  p.mask = x.mask;
+  p.mask_f32 = x.mask_f32;
+  p.sm_z = x.sm[0]; p.sm_h = x.sm[1]; p.sm_q = x.sm[2];
+  {
+    const int per16 = x.mask_f32 ? 4 : 8;  // mask elements per 16 bytes
+    p.mask_vec_ok = x.mask && aligned16(x.mask) && x.sm[0] % per16 == 0 && x.sm[1] % per16 == 0 && x.sm[2] % per16 == 0;
+  }
+  p.mask_h_on = x.sm[1] != 0;
+  p.mask_z_on = x.sm[0] != 0;
+  p.mask_tma = p.mask_vec_ok && !x.mask_f32 && x.sm[2] >= x.n_kv && option("attn_mask_tma", 1);
+  tm[3] = tm[0];
+  if (p.mask_tma) {
+    // a broadcast dimension becomes an extent of 1 (its stride is then never applied)
+    const uint64_t row = (uint64_t)x.sm[2] * 2;
+    const uint64_t dims[4] = {(uint64_t)x.n_kv, (uint64_t)N, (uint64_t)(p.mask_h_on ? H : 1),
+                              (uint64_t)(p.mask_z_on ? Z : 1)};
+    const uint64_t strides[3] = {row, p.mask_h_on ? (uint64_t)x.sm[1] * 2 : row * (uint64_t)N,
+                                 p.mask_z_on ? (uint64_t)x.sm[0] * 2 : row * (uint64_t)N};
+    const uint32_t box[4] = {64, 32, 1, 1};
+    if (encode_tmap_f16_sw128(&tm[3], x.mask, 4, dims, strides, box) != HEXB_OK) {
+      p.mask_tma = 0;  // a layout the tensor map cannot describe: the softmax warps load the mask themselves
+      tm[3] = tm[0];
+    }
+  }
   p.num_q_tiles = (int)((N + BLOCK_M - 1) / BLOCK_M);
   p.scale_log2 = scale_log2;
   p.causal = causal ? 1 : 0;
-  p.out_vec_ok = aligned16(O) && s[9] % 8 == 0 && s[10] % 8 == 0 && s[11] % 8 == 0;
+  {
+    const int per16 = x.out_f32 ? 4 : 8;
+    p.out_vec_ok = aligned16(O) && s[9] % per16 == 0 && s[10] % per16 == 0 && s[11] % per16 == 0;
+  }
   p.v_lbo = (uint32_t)option("attn_v_lbo", cfg::CHUNK_BYTES);
   p.v_sbo = (uint32_t)option("attn_v_sbo", 1024);
   // pairing pays when the tiles differ in length (causal); equal tiles run slightly faster one per CTA
@@ -821,8 +1002,12 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, __half *
   p.ctas_per_bh = p.num_q_tiles / p.tiles_per_cta;
   const int64_t ctas = (int64_t)p.ctas_per_bh * Z * H;
   if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
-  if (two_buffers)
-    attn_fwd_tc2_kernel<HD><<<(unsigned)ctas, THREADS, Cfg2<HD>::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2], p);
+  if (two_buffers && x.mask)
+    attn_fwd_tc2_kernel<HD, true><<<(unsigned)ctas, THREADS, Cfg2<HD>::SMEM_BYTES_MASK, st>>>(tm[0], tm[1], tm[2],
+                                                                                             tm[3], p);
+  else if (two_buffers)
+    attn_fwd_tc2_kernel<HD, false><<<(unsigned)ctas, THREADS, Cfg2<HD>::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2], tm[3],
+                                                                                          p);
   else
     attn_fwd_tc_kernel<HD><<<(unsigned)ctas, THREADS, cfg::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2], p);
   return check_launch("attn_tc");
@@ -854,6 +1039,29 @@ static int attn_check(const void *Q, const void *K, const void *V, void *O, int6
 
 }  // namespace hexb
 
+namespace hexb {
+// Shared body of the fp16-input entry points.
+static int attention_f16_dispatch(const void *Q, const void *K, const void *V, void *Out, int64_t Z, int64_t H,
+                                  int64_t N, int64_t D, const int64_t *s, float sm_scale, int causal,
+                                  const attn::Extra &x, cudaStream_t st) {
+  DeviceInfo di;
+  if (int e = current_device(&di)) return e;
+  const float scale_log2 = sm_scale * 1.44269504f;
+  bool tma_ok = (D == 64 || D == 128) && !option("attn_force_simt", 0) && aligned16(Q) && aligned16(K) &&
+                aligned16(V);
+  for (int i = 0; i < 9 && tma_ok; ++i) tma_ok = s[i] % 8 == 0 && s[i] > 0;
+  if (tma_ok) {
+    if (D == 128)
+      return attn::launch_tc<128>((const __half *)Q, (const __half *)K, (const __half *)V, Out, Z, H, N, s,
+                                  scale_log2, causal, x, st);
+    return attn::launch_tc<64>((const __half *)Q, (const __half *)K, (const __half *)V, Out, Z, H, N, s,
+                               scale_log2, causal, x, st);
+  }
+  return attn::launch_simt<__half>((const __half *)Q, (const __half *)K, (const __half *)V, Out, Z, H, N, D, s,
+                                   scale_log2, causal, x, st);
+}
+}  // namespace hexb
+
 extern "C" int hexb_attention_fwd_f16(const void *Q, const void *K, const void *V, void *Out, int64_t Z,
                                       int64_t H, int64_t N, int64_t D, const int64_t *s, float sm_scale,
                                       int causal, void *stream) {
@@ -861,22 +1069,8 @@ extern "C" int hexb_attention_fwd_f16(const void *Q, const void *K, const void *
   const int c = attn_check(Q, K, V, Out, Z, H, N, D, s, sm_scale);
   if (c == 1) return HEXB_OK;
   if (c) return c;
-  DeviceInfo di;
-  if (int e = current_device(&di)) return e;
-  const float scale_log2 = sm_scale * 1.44269504f;
-  bool tma_ok = (D == 64 || D == 128) && !option("attn_force_simt", 0) && aligned16(Q) && aligned16(K) &&
-                aligned16(V);
-  for (int i = 0; i < 9 && tma_ok; ++i) tma_ok = s[i] % 8 == 0 && s[i] > 0;
-  cudaStream_t st = (cudaStream_t)stream;
-  if (tma_ok) {
-    if (D == 128)
-      return attn::launch_tc<128>((const __half *)Q, (const __half *)K, (const __half *)V, (__half *)Out,
-                                  Z, H, N, s, scale_log2, causal, st);
-    return attn::launch_tc<64>((const __half *)Q, (const __half *)K, (const __half *)V, (__half *)Out, Z,
-                               H, N, s, scale_log2, causal, st);
-  }
-  return attn::launch_simt<__half>((const __half *)Q, (const __half *)K, (const __half *)V, (__half *)Out,
-                                   Z, H, N, D, s, scale_log2, causal, st);
+  const attn::Extra x = {N, 0, nullptr, 0, {0, 0, 0}};
+  return attention_f16_dispatch(Q, K, V, Out, Z, H, N, D, s, sm_scale, causal, x, (cudaStream_t)stream);
 }
 
 extern "C" int hexb_attention_fwd_f32(const float *Q, const float *K, const float *V, float *Out,
@@ -888,6 +1082,37 @@ extern "C" int hexb_attention_fwd_f32(const float *Q, const float *K, const floa
   if (c) return c;
   DeviceInfo di;
   if (int e = current_device(&di)) return e;
-  return attn::launch_simt<float>(Q, K, V, Out, Z, H, N, D, s, sm_scale * 1.44269504f, causal,
+  const attn::Extra x = {N, 1, nullptr, 0, {0, 0, 0}};
+  return attn::launch_simt<float>(Q, K, V, Out, Z, H, N, D, s, sm_scale * 1.44269504f, causal, x,
                                   (cudaStream_t)stream);
+}
+
+extern "C" int hexb_attention_fwd_ex(const hexb_attention_desc *d, void *stream) {
+  using namespace hexb;
+  if (!d) return HEXB_ERR_BAD_ARG;
+  if (d->in_dtype != HEXB_DT_F16 && d->in_dtype != HEXB_DT_F32) return HEXB_ERR_UNSUPPORTED;
+  if (d->out_dtype != HEXB_DT_F16 && d->out_dtype != HEXB_DT_F32) return HEXB_ERR_UNSUPPORTED;
+  if (d->in_dtype == HEXB_DT_F32 && d->out_dtype != HEXB_DT_F32) return HEXB_ERR_UNSUPPORTED;
+  if (d->mask && d->mask_dtype != HEXB_DT_F16 && d->mask_dtype != HEXB_DT_F32) return HEXB_ERR_UNSUPPORTED;
+  if (d->N_KV < 0) return HEXB_ERR_BAD_ARG;
+  const int c = attn_check(d->Q, d->K, d->V, d->Out, d->Z, d->H, d->N_Q, d->D, d->strides, d->sm_scale);
+  if (c == 1) return HEXB_OK;
+  if (c) return c;
+  if (d->N_KV == 0) return HEXB_ERR_BAD_ARG;  // a softmax over no keys has no value
+  if (d->N_KV >= (1ll << 31)) return HEXB_ERR_UNSUPPORTED;
+  attn::Extra x = {d->N_KV, d->out_dtype == HEXB_DT_F32 ? 1 : 0, d->mask, d->mask_dtype == HEXB_DT_F32 ? 1 : 0,
+                   {d->mask_strides[0], d->mask_strides[1], d->mask_strides[2]}};
+  if (d->mask) {
+    for (int i = 0; i < 3; ++i)
+      if (x.sm[i] < 0) return HEXB_ERR_BAD_ARG;
+    if (d->N_Q > 1 && x.sm[2] != 0 && x.sm[2] < d->N_KV) return HEXB_ERR_BAD_ARG;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  if (d->in_dtype == HEXB_DT_F16)
+    return attention_f16_dispatch(d->Q, d->K, d->V, d->Out, d->Z, d->H, d->N_Q, d->D, d->strides, d->sm_scale,
+                                  d->causal, x, st);
+  DeviceInfo di;
+  if (int e = current_device(&di)) return e;
+  return attn::launch_simt<float>((const float *)d->Q, (const float *)d->K, (const float *)d->V, d->Out, d->Z,
+                                  d->H, d->N_Q, d->D, d->strides, d->sm_scale * 1.44269504f, d->causal, x, st);
 }

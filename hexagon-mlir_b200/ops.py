@@ -238,6 +238,67 @@ def attention(q, k, v, out, sm_scale=None, causal: bool = False) -> None:
                                           float(sm_scale), int(bool(causal))), "attention_host")
 
 
+def attention_ex(q, k, v, out, mask=None, sm_scale=None, causal: bool = False) -> None:
+    """out = softmax(q k^T * sm_scale + mask) v on CUDA tensors.
+
+    q, out: [Z, H, N_Q, D]; k, v: [Z, H, N_KV, D]; float16 inputs with a float16 or float32 `out`
+    (the fp16-in / fp32-out form of test/python/mlir/hexkl_attention/input.mlir:5), or all float32.
+    `mask` is additive, float16 or float32, and broadcastable to [Z, H, N_Q, N_KV] with a unit
+    innermost stride; it enters before the row maximum as in the lowering of tm_tensor.attention
+    (qcom_hexagon_backend/lib/Transforms/LowerTmTensor.cpp:126-160).
+    """
+    lib = _lib.load()
+    dev = _same_place(q, k, v, out, mask)
+    if dev.type != "cuda":
+        raise ValueError("attention_ex: CUDA tensors only")
+    if not (q.dim() == k.dim() == v.dim() == out.dim() == 4):
+        raise ValueError("attention_ex: expected [Z, H, N, D] tensors")
+    Z, H, NQ, D = q.shape
+    NKV = k.shape[2]
+    if k.shape != (Z, H, NKV, D) or v.shape != k.shape or out.shape != q.shape:
+        raise ValueError("attention_ex: shapes do not agree")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError("attention_ex: q, k, v must share a dtype")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    d = _lib.AttentionDesc()
+    d.Q, d.K, d.V, d.Out = _ptr(q), _ptr(k), _ptr(v), _ptr(out)
+    d.Z, d.H, d.N_Q, d.N_KV, d.D = Z, H, NQ, NKV, D
+    strides = []
+    for t in (q, k, v, out):
+        if D > 1 and t.stride(3) != 1:
+            raise ValueError("attention_ex: innermost stride must be 1")
+        strides += [t.stride(0), t.stride(1), t.stride(2)]
+    d.strides = (C.c_int64 * 12)(*strides)
+    d.in_dtype, d.out_dtype = _dt(q), _dt(out)
+    if mask is not None:
+        m = mask
+        while m.dim() < 4:
+            m = m.unsqueeze(0)
+        if m.shape[3] != NKV or (NKV > 1 and m.stride(3) != 1):
+            raise ValueError("attention_ex: the mask's last dimension must be N_KV with stride 1")
+        m = m.expand(Z, H, NQ, NKV)
+        d.mask = _ptr(m)
+        d.mask_strides = (C.c_int64 * 3)(m.stride(0), m.stride(1), m.stride(2))
+        d.mask_dtype = _dt(m)
+    else:
+        d.mask = None
+        d.mask_dtype = 0
+    d.sm_scale = float(sm_scale)
+    d.causal = int(bool(causal))
+    with torch.cuda.device(dev):
+        check(lib.hexb_attention_fwd_ex(C.byref(d), _stream(q)), "attention_ex")
+
+
+def sdpa_masked(query, key, value, mask, out) -> None:
+    """tm_tensor.attention ins(Q, K, V, mask) outs(out): rank-3 operands [batch, seq, d], additive mask
+    [batch, seq_q, seq_kv], scale 1/sqrt(d)
+    (qcom_hexagon_backend/include/hexagon/Dialect/TmTensor/IR/TmTensorOps.td:27-55)."""
+    if not (query.dim() == key.dim() == value.dim() == out.dim() == mask.dim() == 3):
+        raise ValueError("sdpa_masked: rank-3 operands expected")
+    attention_ex(query.unsqueeze(1), key.unsqueeze(1), value.unsqueeze(1), out.unsqueeze(1), mask=mask.unsqueeze(1))
+
+
 def silu(x, out) -> None:
     """out = x / (1 + exp(-x)) (reference: test/python/triton/test_silu.py:38-52)."""
     lib = _lib.load()

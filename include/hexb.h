@@ -127,6 +127,31 @@ int hexb_attention_fwd_f32(const float *Q, const float *K, const float *V, float
                            int64_t H, int64_t N_CTX, int64_t D, const int64_t *strides,
                            float sm_scale, int causal, void *stream);
 
+/* ---- generalised forward: separate query and key lengths, fp16 or fp32 output from fp16 inputs, and an
+ * optional additive mask: Out = softmax(Q.K^T * sm_scale + mask) . V, the mask added before the row
+ * maximum exactly as the lowering of tm_tensor.attention does
+ * (qcom_hexagon_backend/lib/Transforms/LowerTmTensor.cpp:126-160 scale, add mask, max, exp, sum, divide;
+ * op definition include/hexagon/Dialect/TmTensor/IR/TmTensorOps.td:27-55: Q [batch, seq_q, d],
+ * K/V [batch, seq_kv, d], mask [batch, seq_q, seq_kv], scale 1/sqrt(d)).  fp16 inputs with fp32 output
+ * is the form of test/python/mlir/hexkl_attention/input.mlir:5 (memref<*xf16> x3, memref<*xf32>).
+ * Tensors are [Z, H, N, D] as for hexb_attention_fwd_f16 (a rank-3 tm_tensor operand is H = 1);
+ * the mask is [Z, H, N_Q, N_KV] addressed as mask + z*ms[0] + h*ms[1] + q*ms[2] + kv in elements of
+ * mask_dtype (a stride of 0 broadcasts that dimension).  mask == NULL: no mask.  causal != 0
+ * additionally drops keys kv > q.  A row whose keys are all masked to -inf yields NaN, as the
+ * reference's exp(-inf - -inf) does.  in_dtype F32 requires out_dtype F32. */
+typedef struct hexb_attention_desc {
+  const void *Q, *K, *V;
+  void *Out;
+  const void *mask;
+  int64_t Z, H, N_Q, N_KV, D;
+  int64_t strides[12];       /* Q, K, V, Out: (z, h, n) each */
+  int64_t mask_strides[3];   /* (z, h, q) */
+  int in_dtype, out_dtype, mask_dtype;
+  float sm_scale;
+  int causal;
+} hexb_attention_desc;
+int hexb_attention_fwd_ex(const hexb_attention_desc *desc, void *stream);
+
 /* ---- SiLU and SwiGLU gating.  Replaces: silu_kernel(x_ptr, output_ptr, BLOCK_SIZE)
  * (test/python/triton/test_silu.py:38-52).  hexb_swiglu_f16: out[r, c] = silu(gu[r, c]) *
  * gu[r, c + cols] for a [rows, 2*cols] gate|up matrix. */

@@ -299,6 +299,45 @@ void oracle_attention_unfused_f16_f32(const f16 *q, const f16 *k, const f16 *v, 
     }
 }
 
+/* tm_tensor.attention as its lowering writes it, qcom_hexagon_backend/lib/Transforms/LowerTmTensor.cpp:70-235:
+ * K^T (:126-130), QK^T by batch_matmul (:133-141), multiply by 1/sqrt(head_dim) (:144-156), add the mask
+ * (:159-162), row maximum from -inf (:166-181), exp(x - max) (:184-200), row sum (:203-213), divide
+ * (:216-230), batch_matmul with V accumulated onto the `outs` operand (:234-238).  Rank-3 operands:
+ * q [batch, seq_q, d], k and v [batch, seq_kv, d], mask [batch, seq_q, seq_kv], out [batch, seq_q, d].
+ * The arithmetic is fp32 here whatever the element type of the operands (the lowering computes in the
+ * operands' own type); `out` must hold the initial value of the accumulator (zeros in the reference's
+ * test, test/Conversion/TmTensorToLinalg/SDPA.mlir:5-13). */
+void oracle_sdpa_masked_f32(const float *q, const float *k, const float *v, const float *mask, float *out,
+                            int64_t batch, int64_t seq_q, int64_t seq_kv, int64_t d) {
+  const float scale = (float)(1.0 / sqrt((double)d));
+#pragma omp parallel for collapse(2)
+  for (int64_t b = 0; b < batch; ++b)
+    for (int64_t i = 0; i < seq_q; ++i) {
+      float *s = (float *)malloc((size_t)seq_kv * sizeof(float));
+      const float *qr = q + (b * seq_q + i) * d;
+      float mx = -INFINITY;
+      for (int64_t n = 0; n < seq_kv; ++n) {
+        const float *kr = k + (b * seq_kv + n) * d;
+        float acc = 0.f;
+        for (int64_t c = 0; c < d; ++c) acc += qr[c] * kr[c];
+        s[n] = acc * scale + mask[(b * seq_q + i) * seq_kv + n];
+        mx = fmaxf(mx, s[n]);
+      }
+      float sum = 0.f;
+      for (int64_t n = 0; n < seq_kv; ++n) {
+        s[n] = expf(s[n] - mx);
+        sum += s[n];
+      }
+      for (int64_t n = 0; n < seq_kv; ++n) s[n] = s[n] / sum;
+      for (int64_t c = 0; c < d; ++c) {
+        float acc = out[(b * seq_q + i) * d + c];
+        for (int64_t n = 0; n < seq_kv; ++n) acc += s[n] * v[(b * seq_kv + n) * d + c];
+        out[(b * seq_q + i) * d + c] = acc;
+      }
+      free(s);
+    }
+}
+
 /* ------------------------------------------------------------------ SiLU
  * silu_kernel, test/python/triton/test_silu.py:48-51: x / (1 + exp((-x).to(f32)).to(x.dtype)). */
 void oracle_silu_f32(const float *x, float *y, int64_t n) {

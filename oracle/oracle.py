@@ -114,6 +114,17 @@ def c_attention_unfused(q, k, v, scale, causal=False):
     return o
 
 
+def c_sdpa_masked(q, k, v, mask):
+    """tm_tensor.attention on rank-3 operands (any float dtype; computed in fp32 from the given values)."""
+    B, SQ, D = q.shape
+    SKV = k.shape[1]
+    qf, kf, vf = (t.float().contiguous() for t in (q, k, v))
+    mf = mask.float().expand(B, SQ, SKV).contiguous()
+    o = torch.zeros(B, SQ, D, dtype=torch.float32)
+    lib().oracle_sdpa_masked_f32(_p(qf), _p(kf), _p(vf), _p(mf), _p(o), _i64(B), _i64(SQ), _i64(SKV), _i64(D))
+    return o
+
+
 def c_silu(x):
     y = torch.empty_like(x)
     fn = lib().oracle_silu_f16 if x.dtype == torch.float16 else lib().oracle_silu_f32

@@ -523,3 +523,130 @@ def test_matmul_nt_vs_oracle(dev, M, N, K, out_dtype):
     c2 = torch.empty(M, N, dtype=out_dtype, device=dev)
     ops.matmul(a.to(dev), w.T.contiguous().to(dev), c2)
     assert O.max_rel_err(c.cpu(), c2.cpu()) < 1e-3
+
+
+# ------------------------------------------------------------------ generalised attention: mask, fp32 out, N_Q != N_KV
+def _sdpa_ref(q, k, v, mask, scale, causal=False):
+    """fp32 torch reference on the (already rounded) inputs."""
+    s = torch.matmul(q.float(), k.float().transpose(-1, -2)) * scale
+    if mask is not None:
+        s = s + mask.float()
+    if causal:
+        nq, nkv = s.shape[-2:]
+        s = s.masked_fill(torch.ones(nq, nkv, dtype=torch.bool).triu(1), float("-inf"))
+    return torch.matmul(torch.softmax(s, dim=-1), v.float())
+
+
+def test_attention_f16_in_f32_out_reference_case(dev):
+    """The fp16-in / fp32-out attention of the reference's MLIR test: 1x1x1024x64, scale 0.5, inputs
+    N(0, 0.5) rounded to 4 decimals, |diff| <= 1e-3 against its unfused CPU check."""
+    g = torch.Generator().manual_seed(11)
+    q, k, v = ((torch.randn(1, 1, 1024, 64, generator=g) * 0.5 * 1e4).round() / 1e4 for _ in range(3))
+    q, k, v = q.half(), k.half(), v.half()
+    out = torch.empty(1, 1, 1024, 64, dtype=torch.float32, device=dev)
+    ops.attention_ex(q.to(dev), k.to(dev), v.to(dev), out, sm_scale=0.5)
+    ref = O.c_attention_unfused(q, k, v, 0.5)
+    assert (out.cpu() - ref).abs().max() <= 1e-3
+    assert hexb200.device_status() == 0
+
+
+@pytest.mark.parametrize("Z,H,NQ,NKV,D", [(2, 3, 256, 256, 64), (1, 2, 384, 640, 128), (2, 2, 100, 77, 64),
+                                          (1, 1, 130, 200, 128), (1, 2, 64, 1024, 64)])
+@pytest.mark.parametrize("mask_dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+def test_attention_masked_f16(dev, Z, H, NQ, NKV, D, mask_dtype, out_dtype):
+    g = torch.Generator().manual_seed(Z + 3 * H + NQ + NKV)
+    q = torch.randn(Z, H, NQ, D, generator=g).half()
+    k, v = (torch.randn(Z, H, NKV, D, generator=g).half() for _ in range(2))
+    mask = torch.randn(Z, H, NQ, NKV, generator=g).to(mask_dtype)
+    out = torch.empty(Z, H, NQ, D, dtype=out_dtype, device=dev)
+    ops.attention_ex(q.to(dev), k.to(dev), v.to(dev), out, mask=mask.to(dev))
+    ref = _sdpa_ref(q, k, v, mask, 1.0 / math.sqrt(D))
+    assert O.max_rel_err(out.cpu(), ref) < REL_F16
+    assert hexb200.device_status() == 0
+
+
+def test_attention_masked_matches_oracle_rank3(dev):
+    """tm_tensor.attention form: rank-3 operands, mask [batch, seq_q, seq_kv], checked against the C oracle."""
+    g = torch.Generator().manual_seed(77)
+    B, SQ, SKV, D = 4, 192, 320, 64
+    q = torch.randn(B, SQ, D, generator=g).half()
+    k, v = (torch.randn(B, SKV, D, generator=g).half() for _ in range(2))
+    mask = torch.randn(B, SQ, SKV, generator=g).half()
+    out = torch.empty(B, SQ, D, dtype=torch.float16, device=dev)
+    ops.sdpa_masked(q.to(dev), k.to(dev), v.to(dev), mask.to(dev), out)
+    ref = O.c_sdpa_masked(q, k, v, mask)
+    assert O.max_rel_err(out.cpu(), ref) < REL_F16
+    # the same in fp32 end to end (CUDA-core path)
+    out32 = torch.empty(B, SQ, D, dtype=torch.float32, device=dev)
+    ops.sdpa_masked(q.float().to(dev), k.float().to(dev), v.float().to(dev), mask.float().to(dev), out32)
+    assert O.max_rel_err(out32.cpu(), ref) < REL_F32
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_attention_additive_causal_mask_equals_causal_flag(dev, D):
+    """-inf above the diagonal as an additive mask gives the causal kernel's result, including key
+    blocks that are masked out entirely."""
+    g = torch.Generator().manual_seed(3)
+    Z, H, N = 1, 2, 512
+    q, k, v = (torch.randn(Z, H, N, D, generator=g).half().to(dev) for _ in range(3))
+    mask = torch.full((N, N), float("-inf")).triu(1).half().to(dev)          # broadcast over Z and H
+    a = torch.empty_like(q)
+    b = torch.empty_like(q)
+    ops.attention_ex(q, k, v, a, mask=mask)
+    ops.attention(q, k, v, b, causal=True)
+    assert O.max_rel_err(a.cpu(), b.cpu()) < 2e-3
+    c = torch.empty_like(q)
+    ops.attention_ex(q, k, v, c, causal=True)                                # flag through the general entry
+    assert torch.equal(c, b)
+    # a leading block fully masked for every row: keys [0, 128) get -inf
+    mask2 = torch.zeros(N, N)
+    mask2[:, :128] = float("-inf")
+    ops.attention_ex(q, k, v, a, mask=mask2.to(dev))
+    ref = _sdpa_ref(q.cpu(), k.cpu(), v.cpu(), mask2, 1.0 / math.sqrt(D))
+    assert O.max_rel_err(a.cpu(), ref) < REL_F16
+    assert hexb200.device_status() == 0
+
+
+def test_attention_fully_masked_row_is_nan_like_the_reference(dev):
+    g = torch.Generator().manual_seed(4)
+    q, k, v = (torch.randn(1, 1, 128, 64, generator=g).half().to(dev) for _ in range(3))
+    mask = torch.zeros(128, 128)
+    mask[5, :] = float("-inf")
+    out = torch.empty(1, 1, 128, 64, dtype=torch.float32, device=dev)
+    ops.attention_ex(q, k, v, out, mask=mask.to(dev))
+    o = out.cpu()[0, 0]
+    assert torch.isnan(o[5]).all()
+    keep = torch.ones(128, dtype=torch.bool)
+    keep[5] = False
+    assert torch.isfinite(o[keep]).all()
+
+
+def test_attention_masked_odd_strides_and_broadcast(dev):
+    """A mask row stride that is not a multiple of 16 bytes (scalar loads) and a [1, 1, 1, N_KV] key bias."""
+    g = torch.Generator().manual_seed(9)
+    Z, H, NQ, NKV, D = 1, 2, 128, 203, 64
+    q = torch.randn(Z, H, NQ, D, generator=g).half()
+    k, v = (torch.randn(Z, H, NKV, D, generator=g).half() for _ in range(2))
+    mask = torch.randn(Z, H, NQ, NKV, generator=g)
+    out = torch.empty(Z, H, NQ, D, dtype=torch.float16, device=dev)
+    ops.attention_ex(q.to(dev), k.to(dev), v.to(dev), out, mask=mask.to(dev))
+    assert O.max_rel_err(out.cpu(), _sdpa_ref(q, k, v, mask, 1.0 / math.sqrt(D))) < REL_F16
+    bias = torch.randn(NKV, generator=g)
+    ops.attention_ex(q.to(dev), k.to(dev), v.to(dev), out, mask=bias.to(dev))
+    assert O.max_rel_err(out.cpu(), _sdpa_ref(q, k, v, bias.view(1, 1, 1, NKV), 1.0 / math.sqrt(D))) < REL_F16
+    assert hexb200.device_status() == 0
+
+
+def test_attention_masked_f32_and_odd_head_dim(dev):
+    g = torch.Generator().manual_seed(10)
+    Z, H, NQ, NKV, D = 2, 2, 75, 131, 40
+    q = torch.randn(Z, H, NQ, D, generator=g)
+    k, v = (torch.randn(Z, H, NKV, D, generator=g) for _ in range(2))
+    mask = torch.randn(Z, H, NQ, NKV, generator=g)
+    out = torch.empty(Z, H, NQ, D, dtype=torch.float32, device=dev)
+    ops.attention_ex(q.to(dev), k.to(dev), v.to(dev), out, mask=mask.to(dev), causal=True)
+    assert O.max_rel_err(out.cpu(), _sdpa_ref(q, k, v, mask, 1.0 / math.sqrt(D), causal=True)) < REL_F32
+    # fp16 tensors of the same odd shape take the CUDA-core path too, with an fp32 result
+    ops.attention_ex(q.half().to(dev), k.half().to(dev), v.half().to(dev), out, mask=mask.half().to(dev))
+    assert O.max_rel_err(out.cpu(), _sdpa_ref(q.half(), k.half(), v.half(), mask.half(), 1.0 / math.sqrt(D))) < REL_F16

@@ -2,6 +2,7 @@
 (tests/golden/make_golden.py) and against the torch values the reference tests assert against.
 Tolerances are the reference tests' own (softmax atol 1e-5 / 1e-3, layer norm 1e-5, rms norm 1e-2,
 matmul 0.2, flash attention allclose defaults, silu 1e-2)."""
+import math
 import os
 
 import numpy as np
@@ -143,3 +144,30 @@ def test_binary_and_math_golden(golden_dir):
     g = load(golden_dir, "math_ops_cos_sin_f32")
     assert torch.allclose(torch.cos(g["in0"]), g["output0"], atol=1e-5)
     assert torch.allclose(torch.sin(g["in0"]), g["output1"], atol=1e-5)
+
+
+# ------------------------------------------------------------------ tm_tensor.attention (masked SDPA)
+@pytest.mark.parametrize("B,SQ,SKV,D", [(2, 4, 4, 8),        # the operand shapes of the reference's SDPA.mlir lit test
+                                        (3, 37, 53, 16), (2, 128, 128, 64)])
+def test_sdpa_masked_oracle_vs_torch(B, SQ, SKV, D):
+    g = torch.Generator().manual_seed(B * 7 + SQ)
+    q, k, v = (torch.randn(B, n, D, generator=g) for n in (SQ, SKV, SKV))
+    mask = torch.randn(B, SQ, SKV, generator=g)
+    mask[:, :, ::3] = -1e4                      # a large negative bias: those keys get zero weight
+    got = O.c_sdpa_masked(q, k, v, mask)
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+    assert torch.allclose(got, ref, rtol=1e-5, atol=1e-6)
+    # the scale constant FileCheck expects for d = 8 (SDPA.mlir:17): 1/sqrt(8) as f32
+    if D == 8:
+        assert abs(np.float32(1.0 / math.sqrt(8)) - np.float32(0.353553385)) < 1e-9
+
+
+def test_sdpa_masked_causal_mask_equals_causal_attention():
+    g = torch.Generator().manual_seed(5)
+    B, S, D = 2, 96, 32
+    q, k, v = (torch.randn(B, S, D, generator=g) for _ in range(3))
+    mask = torch.full((S, S), float("-inf")).triu(1).expand(B, S, S)
+    got = O.c_sdpa_masked(q, k, v, mask)
+    ref = O.c_attention(q.unsqueeze(1).contiguous(), k.unsqueeze(1).contiguous(), v.unsqueeze(1).contiguous(),
+                        1.0 / math.sqrt(D), causal=True).squeeze(1)
+    assert torch.allclose(got, ref, rtol=1e-5, atol=1e-6)
