@@ -383,6 +383,29 @@ def vec_sum(x, out) -> None:
         out.view(-1)[:1].copy_(od)
 
 
+def cumsum(x, out, axis: int = -1, reverse: bool = False) -> None:
+    """out = inclusive prefix sum of x along `axis` (from the far end when `reverse`), contiguous CUDA tensors
+    of float32, float16 (fp32 accumulation) or int32.  Reference: ttx.cumsum / ttx.scan with an addition body
+    (qcom_hexagon_backend/include/hexagon/Dialect/TTX/IR/TTXOps.td:25-75, lib/Transforms/LowerTTX.cpp:75-300)."""
+    lib = _lib.load()
+    dev = _same_place(x, out)
+    if dev.type != "cuda":
+        raise ValueError("cumsum: CUDA tensors only")
+    if x.shape != out.shape or x.dtype != out.dtype or not (x.is_contiguous() and out.is_contiguous()):
+        raise ValueError("cumsum: x and out must be contiguous with equal shape and dtype")
+    if x.dim() == 0:
+        raise ValueError("cumsum: a scalar has no axis")
+    axis = axis % x.dim()
+    dt = {torch.float16: HEXB_DT_F16, torch.float32: HEXB_DT_F32, torch.int32: 3}.get(x.dtype)
+    if dt is None:
+        raise TypeError(f"cumsum: unsupported dtype {x.dtype}")
+    outer = math.prod(x.shape[:axis])
+    inner = math.prod(x.shape[axis + 1:])
+    with torch.cuda.device(dev):
+        check(lib.hexb_cumsum(dt, _ptr(x), _ptr(out), outer, x.shape[axis], inner, int(bool(reverse)), _stream(x)),
+              "cumsum")
+
+
 def rope(x, out, theta: float = 10000.0) -> None:
     """Interleaved-pair rotary embedding of a [B, L, H, D] tensor (reference: test_rope.py:98-190)."""
     lib = _lib.load()

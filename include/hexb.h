@@ -41,7 +41,7 @@ enum {
 };
 
 /* dtype ids: the ids of the reference's raw tensor files (test/utils/dsp/include/tensor.h:26-38) */
-enum { HEXB_DT_F16 = 1, HEXB_DT_F32 = 2 };
+enum { HEXB_DT_F16 = 1, HEXB_DT_F32 = 2, HEXB_DT_I32 = 3 /* hexb_cumsum only */ };
 
 int hexb_version(void);
 const char *hexb_status_string(int status);
@@ -177,6 +177,16 @@ int hexb_binary(int op, int dtype, const void *a, const void *b, void *y, int64_
 int hexb_sum(int dtype, const void *x, void *out, int64_t n, void *stream);
 int hexb_rope(int dtype, const void *x, void *out, int64_t B, int64_t L, int64_t H, int64_t D,
               const int64_t *x_strides, const int64_t *out_strides, float theta, void *stream);
+
+/* ---- cumulative sum along one axis.  The tensor is viewed as [outer, len, inner] (contiguous);
+ * y[o, l, i] = x[o, 0, i] + ... + x[o, l, i], or from the far end when reverse != 0.
+ * dtype = HEXB_DT_F32, HEXB_DT_F16 (fp32 accumulation, one rounding per output) or HEXB_DT_I32
+ * (exact, wrapping).  Replaces: ttx.cumsum {axis}
+ * (qcom_hexagon_backend/include/hexagon/Dialect/TTX/IR/TTXOps.td:61-75, lowering
+ * lib/Transforms/LowerTTX.cpp:179-300) and ttx.scan {axis, reverse} with an addition body
+ * (TTXOps.td:25-40, LowerTTX.cpp:75-176). */
+int hexb_cumsum(int dtype, const void *x, void *y, int64_t outer, int64_t len, int64_t inner,
+                int reverse, void *stream);
 
 /* ---- decoder-only block stack, forward.  Pre-norm blocks:
  *   h = x + Wo . Attn(RMSNorm(x) . Wqkv);  x' = h + Wd . (SiLU(Wg . n) * (Wu . n)), n = RMSNorm(h)

@@ -481,3 +481,36 @@ void oracle_decoder_f16(const f16 *x, f16 *out, const f16 *const *wqkv, const f1
   memcpy(out, cur, (size_t)(T * d) * sizeof(f16));
   free(cur); free(n); free(qkv); free(hq); free(hk); free(hv); free(ho); free(attn); free(h); free(gu); free(act);
 }
+
+/* ------------------------------------------------------------------ cumulative sum
+ * ttx.cumsum {axis} as lowered by qcom_hexagon_backend/lib/Transforms/LowerTTX.cpp:179-300: the first
+ * slice along the axis is the initial partial sum, then for i = 1 .. len-1: p = p + x[.., i, ..];
+ * y[.., i, ..] = p (FileCheck'd in test/Conversion/TtxToLinalg/cumsum_2D.mlir:20-33).  ttx.scan
+ * {reverse = true} with an addition body walks from index len-1 down (LowerTTX.cpp:75-176,
+ * reverse_associative_scan_1D.mlir:26-40).  Tensor viewed as [outer, len, inner].  The float version
+ * keeps the partial sum in fp32; int32 wraps. */
+void oracle_cumsum_f32(const float *x, float *y, int64_t outer, int64_t len, int64_t inner, int reverse) {
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      float p = 0.f;
+      for (int64_t s = 0; s < len; ++s) {
+        const int64_t l = reverse ? len - 1 - s : s;
+        const int64_t idx = (o * len + l) * inner + i;
+        p = s == 0 ? x[idx] : p + x[idx];
+        y[idx] = p;
+      }
+    }
+}
+
+void oracle_cumsum_i32(const int32_t *x, int32_t *y, int64_t outer, int64_t len, int64_t inner, int reverse) {
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      uint32_t p = 0;
+      for (int64_t s = 0; s < len; ++s) {
+        const int64_t l = reverse ? len - 1 - s : s;
+        const int64_t idx = (o * len + l) * inner + i;
+        p += (uint32_t)x[idx];
+        y[idx] = (int32_t)p;
+      }
+    }
+}

@@ -125,6 +125,22 @@ def c_sdpa_masked(q, k, v, mask):
     return o
 
 
+def c_cumsum(x, axis=-1, reverse=False):
+    """ttx.cumsum / additive ttx.scan along `axis`; float inputs are summed in fp32 and returned as fp32."""
+    axis = axis % x.dim()
+    outer = int(np.prod(x.shape[:axis], dtype=np.int64))
+    inner = int(np.prod(x.shape[axis + 1:], dtype=np.int64))
+    if x.dtype == torch.int32:
+        xi = x.contiguous()
+        y = torch.empty_like(xi)
+        lib().oracle_cumsum_i32(_p(xi), _p(y), _i64(outer), _i64(x.shape[axis]), _i64(inner), C.c_int(int(reverse)))
+        return y
+    xf = x.float().contiguous()
+    y = torch.empty_like(xf)
+    lib().oracle_cumsum_f32(_p(xf), _p(y), _i64(outer), _i64(x.shape[axis]), _i64(inner), C.c_int(int(reverse)))
+    return y
+
+
 def c_silu(x):
     y = torch.empty_like(x)
     fn = lib().oracle_silu_f16 if x.dtype == torch.float16 else lib().oracle_silu_f32

@@ -171,3 +171,45 @@ def test_reference_style_launchers():
     kernels.add_2d_kernel[(1,)](a2, b2, o2, NUM_ROWS=64, NUM_COLS=256, enableMultiThreading=True)
     assert torch.allclose(o2, a2 + b2)
     assert hexb200.device_status() == 0
+
+
+# ------------------------------------------------------------------ cumulative sum (ttx.cumsum / additive ttx.scan)
+@pytest.mark.parametrize("shape,axis", [((16, 32), 1), ((256,), 0), ((1000, 4096), 1), ((3, 100003), 1),
+                                        ((1, 5_000_000), 1), ((7, 333, 5), 1), ((64, 128, 96), 0), ((4097,), 0),
+                                        ((2, 3000, 40), 1), ((16384, 2048), 1)])
+@pytest.mark.parametrize("reverse", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.int32])
+def test_cumsum_vs_oracle(shape, axis, reverse, dtype):
+    g = torch.Generator().manual_seed(sum(shape) + axis)
+    if dtype == torch.int32:
+        x = torch.randint(-2 ** 30, 2 ** 30, shape, generator=g, dtype=torch.int32)
+    else:
+        x = torch.rand(*shape, generator=g) - 0.25                     # positive drift: sums grow, no cancellation
+        if dtype == torch.float16:
+            x = x * min(1.0, 2000.0 / shape[axis])                     # keeps the running sum inside fp16's range
+        x = x.to(dtype)
+    out = torch.empty_like(x, device=dev)
+    ops.cumsum(x.to(dev), out, axis=axis, reverse=reverse)
+    ref = O.c_cumsum(x, axis, reverse)
+    if dtype == torch.int32:
+        assert torch.equal(out.cpu(), ref)                            # bit-exact, wrapping
+    else:
+        scale = ref.abs().max().item()
+        tol = 1e-3 if dtype == torch.float32 else 2e-2 / 8            # fp16: half an ulp of the output
+        assert (out.cpu().float() - ref).abs().max().item() <= tol * scale
+
+
+def test_cumsum_segmented_rows_match_single_segment():
+    """A row cut into segments (three launches) gives the sums of the one-CTA-per-row walk."""
+    g = torch.Generator().manual_seed(8)
+    x = torch.randint(-1000, 1000, (2, 1_000_000), generator=g, dtype=torch.int32).to(dev)
+    a = torch.empty_like(x)
+    b = torch.empty_like(x)
+    ops.cumsum(x, a)
+    hexb200.set_option("scan_segments", 1)
+    try:
+        ops.cumsum(x, b)
+    finally:
+        hexb200.set_option("scan_segments", 0)
+    assert torch.equal(a, b)
+    assert torch.equal(a.cpu(), x.cpu().cumsum(1).to(torch.int32))

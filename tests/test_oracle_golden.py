@@ -171,3 +171,21 @@ def test_sdpa_masked_causal_mask_equals_causal_attention():
     ref = O.c_attention(q.unsqueeze(1).contiguous(), k.unsqueeze(1).contiguous(), v.unsqueeze(1).contiguous(),
                         1.0 / math.sqrt(D), causal=True).squeeze(1)
     assert torch.allclose(got, ref, rtol=1e-5, atol=1e-6)
+
+
+# ------------------------------------------------------------------ ttx.cumsum / additive ttx.scan
+@pytest.mark.parametrize("shape,axis", [((16, 32), 1),      # cumsum_2D.mlir
+                                        ((256,), 0),         # the 1-D lit tests
+                                        ((5, 7, 9), 1), ((5, 7, 9), 0)])
+@pytest.mark.parametrize("reverse", [False, True])
+def test_cumsum_oracle_vs_torch(shape, axis, reverse):
+    g = torch.Generator().manual_seed(len(shape) * 10 + axis)
+    x = torch.randn(*shape, generator=g)
+    xi = torch.randint(-2 ** 30, 2 ** 30, shape, generator=g, dtype=torch.int32)
+    for t in (x, xi):
+        got = O.c_cumsum(t, axis, reverse)
+        ref = t.flip(axis).cumsum(axis).flip(axis) if reverse else t.cumsum(axis)
+        if t.dtype == torch.int32:
+            assert torch.equal(got, ref.to(torch.int32))      # wraps like two's complement
+        else:
+            assert torch.allclose(got, ref, rtol=1e-5, atol=1e-5)
