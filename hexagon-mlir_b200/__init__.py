@@ -8,7 +8,7 @@ flash-attention forward, decoder block stack) as hand-written sm_100a CUDA kerne
 The arithmetic lives in libhexb200.so (include/hexb.h); importing this package does not load it,
 the first call does, and a missing library is an error (there is no CPU or PyTorch fallback).
 """
-from . import _lib, kernels, ops, options, report  # noqa: F401
+from . import _lib, gpt2, kernels, ops, options, report  # noqa: F401
 from ._lib import HexbError, device_status, load, set_option  # noqa: F401
 
-__all__ = ["kernels", "ops", "options", "report", "HexbError", "load", "set_option", "device_status"]
+__all__ = ["gpt2", "kernels", "ops", "options", "report", "HexbError", "load", "set_option", "device_status"]

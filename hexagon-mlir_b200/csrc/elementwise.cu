@@ -90,3 +90,66 @@ extern "C" int hexb_swiglu_f16(const void *gu, void *out, int64_t rows, int64_t 
       (const __half *)gu, (__half *)out, rows, (int)(cols / 8));
   return check_launch("swiglu");
 }
+
+// ------------------------------------------------------------------ token + position embedding
+// out[t, :] = wte[ids[t], :] + wpe[t % seq, :]: the first op of the GPT-2 graph the reference compiles
+// through torch-mlir (test/python/torch-mlir/gpt2lmheadmodel.py:143-169).  One warp per token row,
+// 16-byte accesses.  An id outside [0, vocab) writes a zero row and raises the device status word.
+namespace hexb {
+
+static __device__ int g_embed_status = 0;
+
+__global__ void __launch_bounds__(256)
+embedding_kernel(const __half *__restrict__ wte, const __half *__restrict__ wpe, const int64_t *__restrict__ ids,
+                 __half *__restrict__ out, int64_t n_tokens, int64_t seq, int d_model, int64_t vocab, int vec_ok) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= n_tokens) return;
+  const int64_t id = ids[t];
+  const bool ok = id >= 0 && id < vocab;
+  if (!ok && lane == 0) atomicExch(&g_embed_status, (int)HEXB_ERR_BAD_ARG);
+  const __half *te = wte + (ok ? id : 0) * d_model;
+  const __half *pe = wpe + (t % seq) * d_model;
+  __half *o = out + t * d_model;
+  const int nvec = vec_ok ? d_model / 8 : 0;
+  for (int v = lane; v < nvec; v += 32) {
+    Vec16<__half> a, b;
+    a.raw = __ldg(reinterpret_cast<const uint4 *>(te + v * 8));
+    b.raw = __ldg(reinterpret_cast<const uint4 *>(pe + v * 8));
+    float fa[8], fb[8];
+    a.unpack(fa);
+    b.unpack(fb);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) fa[e] = ok ? fa[e] + fb[e] : 0.f;
+    a.pack(fa);
+    *reinterpret_cast<uint4 *>(o + v * 8) = a.raw;
+  }
+  for (int c = nvec * 8 + lane; c < d_model; c += 32)
+    o[c] = ok ? __float2half_rn(__half2float(te[c]) + __half2float(pe[c])) : __float2half_rn(0.f);
+}
+
+int embed_device_status_fetch_and_clear(int *out) {
+  int v = 0, zero = 0;
+  HEXB_CUDA_OK(cudaMemcpyFromSymbol(&v, g_embed_status, sizeof(int)));
+  if (v) HEXB_CUDA_OK(cudaMemcpyToSymbol(g_embed_status, &zero, sizeof(int)));
+  *out = v;
+  return HEXB_OK;
+}
+
+}  // namespace hexb
+
+extern "C" int hexb_embedding_f16(const void *wte, const void *wpe, const int64_t *ids, void *out, int64_t n_tokens,
+                                  int64_t seq, int64_t d_model, int64_t vocab, int64_t n_positions, void *stream) {
+  using namespace hexb;
+  if (n_tokens < 0 || seq <= 0 || d_model < 0 || vocab <= 0 || n_positions < seq) return HEXB_ERR_BAD_ARG;
+  if (n_tokens == 0 || d_model == 0) return HEXB_OK;
+  if (!wte || !wpe || !ids || !out) return HEXB_ERR_BAD_ARG;
+  if (d_model >= (1ll << 31)) return HEXB_ERR_UNSUPPORTED;
+  const int64_t ctas = (n_tokens + 7) / 8;
+  if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
+  const int vec_ok = d_model % 8 == 0 && aligned16(wte) && aligned16(wpe) && aligned16(out);
+  embedding_kernel<<<(unsigned)ctas, 256, 0, (cudaStream_t)stream>>>((const __half *)wte, (const __half *)wpe, ids,
+                                                                    (__half *)out, n_tokens, seq, (int)d_model, vocab,
+                                                                    vec_ok);
+  return check_launch("embedding");
+}

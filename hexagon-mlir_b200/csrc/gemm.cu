@@ -27,7 +27,16 @@ namespace gemm {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int THREADS = 192;
+constexpr int THREADS = 192;      // TMA warp, MMA warp, four epilogue warps
+constexpr int MAX_THREADS = 320;  // ... or eight epilogue warps: two per TMEM lane quarter, each taking half the columns
+// Eight pay when the epilogue is the longer stage of a tile: short K, or an activation to evaluate
+// (measured: 8192 x 2304 x 768 691 -> 799 TFLOP/s, with GELU 508 -> 683); very wide outputs and long K
+// run a little faster with four.
+static inline int launch_threads(int64_t M, int64_t N, int64_t K, int act) {
+  const int64_t forced = option("gemm_epi_warps", 0);
+  if (forced) return forced == 8 ? MAX_THREADS : THREADS;
+  return (act != 0 || (K <= 1024 && M * N <= (1ll << 26))) ? MAX_THREADS : THREADS;
+}
 
 template <int BN, int STAGES>
 struct Cfg {
@@ -97,17 +106,56 @@ __device__ __forceinline__ void store_row_chunk<float>(float *crow, const __half
   }
 }
 
+// Optional per-column bias and activation applied to the accumulators before the residual is added:
+// C = act(A.B + bias) + residual.  act 1: GELU in its tanh form, 0.5 x (1 + tanh(0.797885 x + 0.035677 x^3))
+// (the constants of gelu_kernel, test/python/triton/test_gelu.py:25-54; GPT-2's "gelu_new").
+struct EpiArgs {
+  const __half *bias;  // [N] or null
+  int act;             // 0 none, 1 GELU (tanh form)
+};
+
+__device__ __forceinline__ float gelu_tanh_f32(float x) {
+  const float u = 0.797885f * x + 0.035677f * x * x * x;
+  // 1 + tanh(u) = 2 - 2 / (1 + e^{2u}); the fast division (2 ulp) keeps the epilogue off the slow path the
+  // IEEE one takes once e^{2u} overflows
+  return 0.5f * x * (2.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u)));
+}
+
+__device__ __forceinline__ void apply_bias_act(uint32_t (&acc)[32], const EpiArgs &epi, int col0, int N) {
+  if (epi.bias) {
+    if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(epi.bias + col0) & 15u) == 0) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        Vec16<__half> b;
+        b.raw = __ldg(reinterpret_cast<const uint4 *>(epi.bias + col0 + g * 8));
+        float bf[8];
+        b.unpack(bf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g * 8 + e] = __float_as_uint(__uint_as_float(acc[g * 8 + e]) + bf[e]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        if (col0 + e < N) acc[e] = __float_as_uint(__uint_as_float(acc[e]) + __half2float(__ldg(epi.bias + col0 + e)));
+    }
+  }
+  if (epi.act == 1) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(gelu_tanh_f32(__uint_as_float(acc[e])));
+  }
+}
+
 // EPI == 1 (SwiGLU, BN = 256, fp16 out): B is a [K, 2*N] gate|up matrix; a tile's B operand is made
 // of 128 gate columns [col0, col0+128) and the 128 up columns [N+col0, N+col0+128), so accumulator
 // columns c and 128+c belong to output column col0+c and the epilogue writes silu(gate) * up.
 // BT: B is given transposed, Bt[N, K] row-major (C = A @ Bt^T): it is then the K-major operand form,
 // loaded as 128-row x 64-k boxes like A.
 template <int BN, int STAGES, typename OutT, int EPI = 0, bool BT = false>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(MAX_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
                int64_t ldr, int tiles_m, int tiles_n, int vec_ok, uint32_t b_lbo, uint32_t b_sbo,
-               int full_items, int split) {
+               int full_items, int split, const EpiArgs epi) {
   using cfg = Cfg<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
@@ -134,7 +182,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       tc::mbar_init(tfull_bar(a), 1);
-      tc::mbar_init(tempty_bar(a), 4);
+      tc::mbar_init(tempty_bar(a), (blockDim.x >> 5) - 2);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     tc::fence_barrier_init();
@@ -240,8 +288,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------ epilogue (warps 2..5 or 2..9)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const int halves = ((blockDim.x >> 5) - 2) >> 2, half = (warp - 2) >> 2;  // column share of this warp
     int t = 0;
     for (int item = blockIdx.x; item < num_items; item += gridDim.x, ++t) {
       const Item w = item_of(item);
@@ -254,8 +303,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       OutT *crow = C + (int64_t)row * ldc;
       const __half *rrow = R ? R + (int64_t)row * ldr : nullptr;
       if constexpr (EPI == 1) {
+        const int nch = BN / 64 / halves;
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
+        for (int c = half * nch; c < (half + 1) * nch; ++c) {
           uint32_t g[32], u[32];
           tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), g);
           tc::tmem_ld_32x32(taddr + (uint32_t)(BN / 2 + c * 32), u);
@@ -263,18 +313,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const float gv = __uint_as_float(g[e]);
-            g[e] = __float_as_uint((gv / (1.0f + __expf(-gv))) * __uint_as_float(u[e]));
+            g[e] = __float_as_uint(__fdividef(gv, 1.0f + __expf(-gv)) * __uint_as_float(u[e]));
           }
           const int col0 = w.col0 + c * 32;
           if (row < M && col0 < N) store_row_chunk<OutT>(crow, nullptr, g, col0, N, vec_ok != 0);
         }
       } else {
+        const int nch = w.width / 32 / halves;  // widths are multiples of 64
 #pragma unroll 1
-        for (int c = 0; c < w.width / 32; ++c) {
+        for (int c = half * nch; c < (half + 1) * nch; ++c) {
           uint32_t v[32];
           tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
           tc::tmem_ld_wait();
           const int col0 = w.col0 + c * 32;
+          if constexpr (EPI == 2) apply_bias_act(v, epi, col0, N);
           if (row < M && col0 < N) store_row_chunk<OutT>(crow, rrow, v, col0, N, vec_ok != 0);
         }
       }
@@ -303,7 +355,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const __half *__restrict__ A, const __half *__restrict__ B, OutT *__restrict__ C,
                  const __half *__restrict__ R, int64_t M, int64_t N, int64_t K, int64_t lda,
-                 int64_t ldb, int64_t ldc, int64_t ldr, int bt) {
+                 int64_t ldb, int64_t ldc, int64_t ldr, int bt, const EpiArgs epi) {
   __shared__ float As[16][17], Bs[16][17];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int64_t row = (int64_t)blockIdx.y * 16 + ty, col = (int64_t)blockIdx.x * 16 + tx;
@@ -317,6 +369,8 @@ gemm_simt_kernel(const __half *__restrict__ A, const __half *__restrict__ B, Out
     __syncthreads();
   }
   if (row < M && col < N) {
+    if (epi.bias) acc += __half2float(epi.bias[col]);
+    if (epi.act == 1) acc = gelu_tanh_f32(acc);
     if (R) acc += __half2float(R[row * ldr + col]);
     C[row * ldc + col] = from_f32<OutT>(acc);
   }
@@ -341,10 +395,10 @@ constexpr int TMEM_COLS = 512;
 }  // namespace pair
 
 template <typename OutT, int EPI, bool BT = false>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MAX_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
-                    int64_t ldr, int tiles_m, int tiles_n, int vec_ok) {
+                    int64_t ldr, int tiles_m, int tiles_n, int vec_ok, const EpiArgs epi) {
   using namespace pair;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
@@ -372,7 +426,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       tc::mbar_init(tfull_bar(a), 1);
-      tc::mbar_init(tempty_bar(a), 8);  // four epilogue warps in each CTA of the pair
+      tc::mbar_init(tempty_bar(a), 2 * ((blockDim.x >> 5) - 2));  // the epilogue warps of both CTAs of the pair
     }
     *abort_flag = 0;
     tc::fence_barrier_init();
@@ -452,8 +506,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    // ------------------------------------------------------------ epilogue (warps 2..5 or 2..9, both CTAs)
     const int q = warp & 3;
+    const int halves = ((blockDim.x >> 5) - 2) >> 2, half = (warp - 2) >> 2;
     int t = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++t) {
       const int tm = tile % tiles_m, col_base = (tile / tiles_m) * OUT_COLS;
@@ -465,8 +520,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       OutT *crow = C + (int64_t)row * ldc;
       const __half *rrow = R ? R + (int64_t)row * ldr : nullptr;
       if constexpr (EPI == 1) {
+        const int nch = BN / 64 / halves;
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
+        for (int c = half * nch; c < (half + 1) * nch; ++c) {
           uint32_t g[32], u[32];
           tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), g);
           tc::tmem_ld_32x32(taddr + (uint32_t)(BN / 2 + c * 32), u);
@@ -474,18 +530,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const float gv = __uint_as_float(g[e]);
-            g[e] = __float_as_uint((gv / (1.0f + __expf(-gv))) * __uint_as_float(u[e]));
+            g[e] = __float_as_uint(__fdividef(gv, 1.0f + __expf(-gv)) * __uint_as_float(u[e]));
           }
           const int col0 = col_base + c * 32;
           if (row < M && col0 < N) store_row_chunk<OutT>(crow, nullptr, g, col0, N, vec_ok != 0);
         }
       } else {
+        const int nch = BN / 32 / halves;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = half * nch; c < (half + 1) * nch; ++c) {
           uint32_t v[32];
           tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
           tc::tmem_ld_wait();
           const int col0 = col_base + c * 32;
+          if constexpr (EPI == 2) apply_bias_act(v, epi, col0, N);
           if (row < M && col0 < N) store_row_chunk<OutT>(crow, rrow, v, col0, N, vec_ok != 0);
         }
       }
@@ -509,7 +567,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 }
 
 template <typename OutT, int EPI, bool BT = false>
-static int launch_tc_pair(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M, int N,
+static int launch_tc_pair(const EpiArgs &epi, const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M, int N,
                           int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count, cudaStream_t st) {
   static bool attr_done[64] = {};
   int dev = 0;
@@ -523,12 +581,13 @@ static int launch_tc_pair(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *
   const int tiles_m = (M + 255) / 256, tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
   const int tiles = tiles_m * tiles_n;
   const int clusters = tiles < sm_count / 2 ? tiles : sm_count / 2;
-  kern<<<2 * clusters, THREADS, pair::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok);
+  kern<<<2 * clusters, launch_threads(M, N, K, EPI == 1 ? 1 : epi.act), pair::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok,
+                                                        epi);
   return check_launch("gemm_tc_pair");
 }
 
 template <int BN, int STAGES, typename OutT, int EPI = 0, bool BT = false>
-static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M,
+static int launch_tc(const EpiArgs &epi, const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M,
                      int N, int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count,
                      cudaStream_t st) {
   using cfg = Cfg<BN, STAGES>;
@@ -554,14 +613,16 @@ static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, co
   const int grid = items < sm_count ? items : sm_count;
   const uint32_t lbo = (uint32_t)option("gemm_b_lbo", BK * 128);
   const uint32_t sbo = (uint32_t)option("gemm_b_sbo", 1024);
-  kern<<<grid, THREADS, cfg::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n,
-                                               vec_ok, lbo, sbo, full_items, split);
+  kern<<<grid, launch_threads(M, N, K, EPI == 1 ? 1 : epi.act), cfg::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n,
+                                               vec_ok, lbo, sbo, full_items, split, epi);
   return check_launch("gemm_tc");
 }
 
-template <typename OutT, bool BT = false>
+// EPI 0: plain product (+ residual); EPI 2: bias / activation applied in the epilogue as well.
+template <typename OutT, bool BT = false, int EPI = 0>
 static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *R, int64_t M, int64_t N,
-                       int64_t K, int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t st) {
+                       int64_t K, int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t st,
+                       const EpiArgs epi = EpiArgs{nullptr, 0}) {
   DeviceInfo di;
   if (int s = current_device(&di)) return s;
   const int64_t ldr = ldc;
@@ -571,7 +632,7 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
   if (!tc_ok) {
     dim3 grid((unsigned)((N + 15) / 16), (unsigned)((M + 15) / 16));
     if (grid.y > 65535) return HEXB_ERR_UNSUPPORTED;
-    gemm_simt_kernel<OutT><<<grid, 256, 0, st>>>(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, BT ? 1 : 0);
+    gemm_simt_kernel<OutT><<<grid, 256, 0, st>>>(A, B, C, R, M, N, K, lda, ldb, ldc, ldr, BT ? 1 : 0, epi);
     return check_launch("gemm_simt");
   }
   CUtensorMap tmA, tmB;
@@ -604,15 +665,15 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
   // CTA-pair kernel for problems with at least one 256 x 256 tile per pair of SMs
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
   if (option("gemm_bn", 0) == 0 && option("gemm_pair", 1) && pair_tiles >= di.sm_count / 2)
-    return launch_tc_pair<OutT, 0, BT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+    return launch_tc_pair<OutT, EPI, BT>(epi, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
   if (BT && bn == 64) bn = 128;  // the transposed form loads Bt in 128-row boxes
   switch (bn) {
     case 64:
-      return launch_tc<64, 8, OutT, 0, false>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<64, 8, OutT, EPI, false>(epi, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
     case 128:
-      return launch_tc<128, 6, OutT, 0, BT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<128, 6, OutT, EPI, BT>(epi, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
     default:
-      return launch_tc<256, 4, OutT, 0, BT>(tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<256, 4, OutT, EPI, BT>(epi, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
   }
 }
 
@@ -660,6 +721,35 @@ extern "C" int hexb_matmul_f16_nt(const void *A, const void *Bt, void *C, const 
                                         M, N, K, lda, ldbt, ldc, (cudaStream_t)stream);
 }
 
+extern "C" int hexb_linear_f16(const void *A, const void *W, const void *bias, const void *residual, void *C,
+                               int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc,
+                               int w_transposed, int act, int out_dtype, void *stream) {
+  using namespace hexb;
+  if (M < 0 || N < 0 || K < 0) return HEXB_ERR_BAD_ARG;
+  if (out_dtype != HEXB_DT_F16 && out_dtype != HEXB_DT_F32) return HEXB_ERR_UNSUPPORTED;
+  if (act != 0 && act != 1) return HEXB_ERR_UNSUPPORTED;
+  if (M == 0 || N == 0) return HEXB_OK;
+  if (!C || (K > 0 && (!A || !W))) return HEXB_ERR_BAD_ARG;
+  if (lda < K || ldc < N || ldw < (w_transposed ? K : N)) return HEXB_ERR_BAD_ARG;
+  const gemm::EpiArgs epi{(const __half *)bias, act};
+  const __half *a = (const __half *)A, *w = (const __half *)W, *r = (const __half *)residual;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!bias && !act) {  // nothing for the epilogue to add: the plain kernels
+    if (out_dtype == HEXB_DT_F16) {
+      if (w_transposed) return gemm::matmul_impl<__half, true>(a, w, (__half *)C, r, M, N, K, lda, ldw, ldc, st);
+      return gemm::matmul_impl<__half, false>(a, w, (__half *)C, r, M, N, K, lda, ldw, ldc, st);
+    }
+    if (w_transposed) return gemm::matmul_impl<float, true>(a, w, (float *)C, r, M, N, K, lda, ldw, ldc, st);
+    return gemm::matmul_impl<float, false>(a, w, (float *)C, r, M, N, K, lda, ldw, ldc, st);
+  }
+  if (out_dtype == HEXB_DT_F16) {
+    if (w_transposed) return gemm::matmul_impl<__half, true, 2>(a, w, (__half *)C, r, M, N, K, lda, ldw, ldc, st, epi);
+    return gemm::matmul_impl<__half, false, 2>(a, w, (__half *)C, r, M, N, K, lda, ldw, ldc, st, epi);
+  }
+  if (w_transposed) return gemm::matmul_impl<float, true, 2>(a, w, (float *)C, r, M, N, K, lda, ldw, ldc, st, epi);
+  return gemm::matmul_impl<float, false, 2>(a, w, (float *)C, r, M, N, K, lda, ldw, ldc, st, epi);
+}
+
 extern "C" int hexb_matmul_swiglu_f16(const void *A, const void *B_gate_up, void *out, int64_t M, int64_t F,
                                       int64_t K, int64_t lda, int64_t ldb, int64_t ldo, void *stream) {
   using namespace hexb;
@@ -687,9 +777,9 @@ extern "C" int hexb_matmul_swiglu_f16(const void *A, const void *B_gate_up, void
   }
   const int vec_ok = (ldo % 8 == 0) && aligned16(out);
   if (option("gemm_pair", 1) && ((M + 255) / 256) * ((F + 127) / 128) >= di.sm_count / 2)
-    return launch_tc_pair<__half, 1>(tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
+    return launch_tc_pair<__half, 1>(gemm::EpiArgs{nullptr, 0}, tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
                                      di.sm_count, (cudaStream_t)stream);
-  return launch_tc<256, 4, __half, 1>(tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
+  return launch_tc<256, 4, __half, 1>(gemm::EpiArgs{nullptr, 0}, tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
                                       di.sm_count, (cudaStream_t)stream);
 }
 

@@ -61,6 +61,7 @@ int gemm_device_status_fetch_and_clear(int *out);
 int attn_device_status_fetch_and_clear(int *out);
 int norm_device_status_fetch_and_clear(int *out);
 int softmax_device_status_fetch_and_clear(int *out);
+int embed_device_status_fetch_and_clear(int *out);
 
 }  // namespace hexb
 
@@ -68,11 +69,12 @@ extern "C" int hexb_device_status(int *out) {
   using namespace hexb;
   if (!out) return HEXB_ERR_BAD_ARG;
   HEXB_CUDA_OK(cudaDeviceSynchronize());
-  int v[4] = {0, 0, 0, 0};
+  int v[5] = {0, 0, 0, 0, 0};
   if (int s = gemm_device_status_fetch_and_clear(&v[0])) return s;
   if (int s = attn_device_status_fetch_and_clear(&v[1])) return s;
   if (int s = norm_device_status_fetch_and_clear(&v[2])) return s;
   if (int s = softmax_device_status_fetch_and_clear(&v[3])) return s;
-  *out = v[0] ? v[0] : v[1] ? v[1] : v[2] ? v[2] : v[3];
+  if (int s = embed_device_status_fetch_and_clear(&v[4])) return s;
+  *out = v[0] ? v[0] : v[1] ? v[1] : v[2] ? v[2] : v[3] ? v[3] : v[4];
   return HEXB_OK;
 }

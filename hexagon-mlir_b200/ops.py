@@ -179,6 +179,54 @@ def matmul_nt(a, bt, c, residual=None) -> None:
                                      _stream(a)), "matmul_nt")
 
 
+def linear(a, w, c, bias=None, residual=None, act: str = "none", w_transposed: bool = False) -> None:
+    """c = act(a @ w + bias) + residual in one launch; w is [K, N], or [N, K] with w_transposed.
+    act: "none" or "gelu_tanh".  Reference: the addmm / gelu / add chains of the GPT-2 graph,
+    test/python/torch-mlir/gpt2lmheadmodel.py:143-169."""
+    lib = _lib.load()
+    _same_place(a, w, c, bias, residual)
+    if a.dtype != torch.float16 or w.dtype != torch.float16:
+        raise TypeError("linear: A and W must be float16")
+    M, K, lda = _rows2d(a, "A")
+    if w_transposed:
+        N, K2, ldw = _rows2d(w, "W")
+    else:
+        K2, N, ldw = _rows2d(w, "W")
+    M2, N2, ldc = _rows2d(c, "C")
+    if K != K2 or M != M2 or N != N2:
+        raise ValueError("linear: shapes do not agree")
+    if bias is not None and (bias.dtype != torch.float16 or bias.shape != (N,) or not bias.is_contiguous()):
+        raise ValueError("linear: bias must be a contiguous float16 [N] vector")
+    if residual is not None and (residual.dtype != torch.float16 or residual.shape != c.shape
+                                 or residual.stride(0) != c.stride(0)):
+        raise ValueError("linear: residual must be float16 with C's shape and leading dimension")
+    acts = {"none": 0, "gelu_tanh": 1}
+    if act not in acts:
+        raise ValueError(f"linear: unknown activation {act!r}")
+    with torch.cuda.device(a.device):
+        check(lib.hexb_linear_f16(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(c), M, N, K, lda, ldw, ldc,
+                                  int(bool(w_transposed)), acts[act], _dt(c), _stream(a)), "linear")
+
+
+def embedding(wte, wpe, ids, out) -> None:
+    """out[b, s, :] = wte[ids[b, s], :] + wpe[s, :] for float16 tables and int64 ids [batch, seq]."""
+    lib = _lib.load()
+    _same_place(wte, wpe, ids, out)
+    if wte.dtype != torch.float16 or wpe.dtype != torch.float16 or out.dtype != torch.float16:
+        raise TypeError("embedding: tables and output must be float16")
+    if ids.dtype != torch.int64 or ids.dim() != 2:
+        raise TypeError("embedding: ids must be an int64 [batch, seq] tensor")
+    B, S = ids.shape
+    V, Dm = wte.shape
+    if wpe.shape[1] != Dm or out.shape != (B, S, Dm) or wpe.shape[0] < S:
+        raise ValueError("embedding: shapes do not agree")
+    if not all(t.is_contiguous() for t in (wte, wpe, ids, out)):
+        raise ValueError("embedding: contiguous tensors expected")
+    with torch.cuda.device(wte.device):
+        check(lib.hexb_embedding_f16(_ptr(wte), _ptr(wpe), _ptr(ids), _ptr(out), B * S, S, Dm, V, wpe.shape[0],
+                                     _stream(wte)), "embedding")
+
+
 def matmul_swiglu(a, b_gate_up, out) -> None:
     """out = silu(a @ b[:, :F]) * (a @ b[:, F:]) for a [M, K], b [K, 2F], out [M, F]; float16 CUDA tensors."""
     lib = _lib.load()

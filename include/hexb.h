@@ -96,6 +96,16 @@ int hexb_matmul_f16_nt(const void *A, const void *Bt, void *C, const void *resid
                        int64_t N, int64_t K, int64_t lda, int64_t ldbt, int64_t ldc, int out_dtype,
                        void *stream);
 
+/* Linear layer in one launch: C = act(A @ W + bias) + residual.  W is [K, N] (ldw >= N), or [N, K]
+ * (ldw >= K) when w_transposed != 0; bias is a [N] fp16 vector or NULL; residual as for
+ * hexb_matmul_f16; act 0 = none, 1 = GELU in the tanh form of gelu_kernel
+ * (test/python/triton/test_gelu.py:25-54).  Replaces: the addmm / gelu / add chains of the GPT-2 graph
+ * the reference compiles through torch-mlir (test/python/torch-mlir/gpt2lmheadmodel.py:143-169) and
+ * lowers op by op to linalg generics around hexkl matmuls. */
+int hexb_linear_f16(const void *A, const void *W, const void *bias, const void *residual, void *C,
+                    int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc,
+                    int w_transposed, int act, int out_dtype, void *stream);
+
 /* Gate/up projection with the SwiGLU gating fused into the epilogue:
  *   out[M, F] = silu(A @ B[:, 0:F]) * (A @ B[:, F:2F]),  B = [K, 2F] row-major (columns gate|up).
  * fp32 accumulation and gating, one rounding to fp16.  Composed from matmul
@@ -177,6 +187,14 @@ int hexb_binary(int op, int dtype, const void *a, const void *b, void *y, int64_
 int hexb_sum(int dtype, const void *x, void *out, int64_t n, void *stream);
 int hexb_rope(int dtype, const void *x, void *out, int64_t B, int64_t L, int64_t H, int64_t D,
               const int64_t *x_strides, const int64_t *out_strides, float theta, void *stream);
+
+/* ---- token + position embedding: out[t, :] = wte[ids[t], :] + wpe[t % seq, :] for fp16 tables
+ * wte [vocab, d_model], wpe [n_positions, d_model] and int64 ids [n_tokens] (n_tokens = batch * seq).
+ * An id outside [0, vocab) writes a zero row and makes hexb_device_status report HEXB_ERR_BAD_ARG.
+ * Replaces: the two embedding gathers and their sum at the top of the GPT-2 graph
+ * (test/python/torch-mlir/gpt2lmheadmodel.py:143-169). */
+int hexb_embedding_f16(const void *wte, const void *wpe, const int64_t *ids, void *out, int64_t n_tokens,
+                       int64_t seq, int64_t d_model, int64_t vocab, int64_t n_positions, void *stream);
 
 /* ---- cumulative sum along one axis.  The tensor is viewed as [outer, len, inner] (contiguous);
  * y[o, l, i] = x[o, 0, i] + ... + x[o, l, i], or from the far end when reverse != 0.

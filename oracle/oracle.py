@@ -254,6 +254,33 @@ def torch_decoder(x, weights, n_heads, head_dim, d_ff, batch, seq, eps, store_dt
 
 
 # ------------------------------------------------------------------ seeded inputs of the five configurations
+def torch_gpt2(sd, n_layer, n_head, eps, input_ids):
+    """GPT2LMHeadModel forward in plain fp32 torch from a Hugging Face state dict: what the reference runs
+    on x86 as its expected result (test/python/torch-mlir/gpt2lmheadmodel.py:30-33, 143-169).  Conv1D is
+    x @ W + b with W [in, out]; GELU is the tanh form; attention is causal with scale 1/sqrt(head_dim);
+    the LM head is tied to the token embedding."""
+    f = {k: v.float() for k, v in sd.items()}
+    B, S = input_ids.shape
+    x = f["transformer.wte.weight"][input_ids] + f["transformer.wpe.weight"][:S]
+    d = x.shape[-1]
+    hd = d // n_head
+    for i in range(n_layer):
+        p = f"transformer.h.{i}."
+        h = F.layer_norm(x, (d,), f[p + "ln_1.weight"], f[p + "ln_1.bias"], eps)
+        qkv = h @ f[p + "attn.c_attn.weight"] + f[p + "attn.c_attn.bias"]
+        q, k, v = (t.view(B, S, n_head, hd).transpose(1, 2) for t in qkv.split(d, dim=-1))
+        s = (q @ k.transpose(-1, -2)) / math.sqrt(hd)
+        s = s.masked_fill(torch.ones(S, S, dtype=torch.bool).triu(1), float("-inf"))
+        a = (torch.softmax(s, dim=-1) @ v).transpose(1, 2).reshape(B, S, d)
+        x = x + a @ f[p + "attn.c_proj.weight"] + f[p + "attn.c_proj.bias"]
+        h = F.layer_norm(x, (d,), f[p + "ln_2.weight"], f[p + "ln_2.bias"], eps)
+        h = h @ f[p + "mlp.c_fc.weight"] + f[p + "mlp.c_fc.bias"]
+        h = 0.5 * h * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (h + 0.044715 * h ** 3)))
+        x = x + h @ f[p + "mlp.c_proj.weight"] + f[p + "mlp.c_proj.bias"]
+    x = F.layer_norm(x, (d,), f["transformer.ln_f.weight"], f["transformer.ln_f.bias"], eps)
+    return x @ f["transformer.wte.weight"].T
+
+
 def _gen(seed):
     return torch.Generator(device="cpu").manual_seed(seed)
 

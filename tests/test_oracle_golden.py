@@ -189,3 +189,24 @@ def test_cumsum_oracle_vs_torch(shape, axis, reverse):
             assert torch.equal(got, ref.to(torch.int32))      # wraps like two's complement
         else:
             assert torch.allclose(got, ref, rtol=1e-5, atol=1e-5)
+
+
+# ------------------------------------------------------------------ GPT-2 (two layers, random weights)
+def test_gpt2_oracle_matches_transformers():
+    """Pins the plain-torch GPT-2 restatement on Hugging Face's GPT2LMHeadModel, the model the reference
+    test instantiates (with pretrained weights, which need a network; random weights here)."""
+    transformers = pytest.importorskip("transformers")
+    import hexb200
+    from hexb200 import gpt2
+    cfg = gpt2.GPT2Config(n_layer=2, n_embd=64, n_head=4, n_positions=32, vocab_size=101)
+    sd = gpt2.random_state_dict(cfg, seed=3, dtype=torch.float32)
+    hf_cfg = transformers.GPT2Config(n_layer=cfg.n_layer, n_embd=cfg.n_embd, n_head=cfg.n_head,
+                                     n_positions=cfg.n_positions, vocab_size=cfg.vocab_size)
+    model = transformers.GPT2LMHeadModel(hf_cfg).eval()
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    assert not unexpected and all(("attn.bias" in m or "masked_bias" in m or m == "lm_head.weight") for m in missing)
+    ids = torch.randint(0, cfg.vocab_size, (2, 17), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = model(input_ids=ids).logits
+    got = O.torch_gpt2(sd, cfg.n_layer, cfg.n_head, cfg.layer_norm_epsilon, ids)
+    assert torch.allclose(got, ref, rtol=1e-4, atol=1e-5)
