@@ -273,8 +273,37 @@ class DecoderWL(Workload):
                 "l2": "weights + activations (1.1 GiB) exceed L2"}
 
 
+class GPT2WL(Workload):
+    """GPT2LMHeadModel cut to two layers (the reference's largest test), random fp16 weights, batch 8 x 1024
+    tokens, fp16 logits: embedding + 2 x 7 launches + final norm + tied LM head."""
+    name, unit, bound, dtype = "gpt2", "TFLOP/s", "tensor", "f16"
+    B, S = 8, 1024
+
+    def __init__(self, dev):
+        from hexb200 import gpt2
+
+        self.cfg = gpt2.GPT2Config()
+        self.runner = gpt2.GPT2Runner(self.cfg, gpt2.random_state_dict(self.cfg, seed=1006), device=dev)
+        g = torch.Generator().manual_seed(1006)
+        ids = torch.randint(0, self.cfg.vocab_size, (self.B, self.S), generator=g)
+        self.host = (ids,)
+        self.ids = ids.to(dev)
+        self.launches_per_step = self.runner.launches()
+
+    def step(self, i):
+        self.runner.forward(self.ids, logits_dtype=torch.float16)
+
+    def work_per_step(self):
+        return self.runner.flops(self.B, self.S)
+
+    def describe(self):
+        return {"workload": "GPT-2 small geometry, 2 layers, fp16, batch 8 x seq 1024, logits [8192, 50257] fp16 "
+                            "(the reference's torch-mlir GPT-2 test, random weights)",
+                "l2": "wte (77 MB) + logits (823 MB) exceed L2"}
+
+
 WORKLOADS = {"layernorm": LayerNormWL, "softmax": SoftmaxWL, "gemm": GemmWL, "attention": AttentionWL,
-             "decoder": DecoderWL}
+             "decoder": DecoderWL, "gpt2": GPT2WL}
 
 
 def time_steps(wl, steps, warmup, barrier, use_graph=True):
@@ -354,6 +383,14 @@ def cpu_reference_step(name):
         q, k, v = (t.float() for t in O.make_attention_inputs(1, 4, 4096, 128))
         return (lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True), 4.0 * 4 * 4096 * 4096 * 128 / 2,
                 "4 of 128 (batch, head) pairs, F.scaled_dot_product_attention(is_causal=True) fp32 on CPU")
+    if name == "gpt2":
+        from hexb200 import gpt2
+        cfg = gpt2.GPT2Config()
+        sd = gpt2.random_state_dict(cfg, seed=1006)
+        ids = torch.randint(0, cfg.vocab_size, (1, 256), generator=torch.Generator().manual_seed(1006))
+        work = gpt2.GPT2Runner.flops_of(cfg, 1, 256)
+        return (lambda: O.torch_gpt2(sd, cfg.n_layer, cfg.n_head, cfg.layer_norm_epsilon, ids), work,
+                "1 sequence x 256 tokens, fp32 torch on the fp16-rounded weights")
     if name == "decoder":
         x, ws = O.make_decoder_inputs(1, 2048, 16, 8192, 1, 1024)
         T = 1024
@@ -431,6 +468,18 @@ def e2e_generic(wl, steps):
         o = torch.empty_like(q).pin_memory()
         call = lambda: ops.attention(q, k, v, o, causal=True)
         h2d, d2h = 3 * q.numel() * 2, q.numel() * 2
+    elif wl.name == "gpt2":
+        (ids,) = wl.host
+        idp = ids.pin_memory()
+        last = torch.empty(wl.B, wl.cfg.vocab_size, dtype=torch.float16).pin_memory()
+
+        def call():  # prompt ids up, the last position's logits back (what the reference's top-5 check reads)
+            wl.ids.copy_(idp, non_blocking=True)
+            logits = wl.runner.forward(wl.ids, logits_dtype=torch.float16)
+            last.copy_(logits[:, -1, :], non_blocking=True)
+            torch.cuda.synchronize()
+
+        h2d, d2h = ids.numel() * 8, last.numel() * 2
     else:
         (x,) = wl.host
         xp, outp = x.pin_memory(), torch.empty_like(x).pin_memory()
@@ -570,7 +619,7 @@ def main():
             if name == args.workload:
                 continue
             w2 = WORKLOADS[name](dev)
-            k2 = {"softmax": 200, "gemm": 50, "attention": 10, "decoder": 5}.get(name, 20)
+            k2 = {"softmax": 200, "gemm": 50, "attention": 10, "decoder": 5, "gpt2": 10}.get(name, 20)
             ms2, _, _, _ = time_steps(w2, k2, 3, lambda: None, not args.eager)
             ms2 /= k2
             sc = 1e9 if w2.bound == "hbm" else 1e12

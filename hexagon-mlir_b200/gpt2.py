@@ -134,9 +134,13 @@ class GPT2Runner:
 
     def flops(self, B: int, S: int) -> float:
         """Matmul and attention FLOPs of one forward pass (causal attention counted at half the square)."""
-        d, L, V = self.cfg.n_embd, self.cfg.n_layer, self.cfg.vocab_size
+        return self.flops_of(self.cfg, B, S)
+
+    @staticmethod
+    def flops_of(cfg: GPT2Config, B: int, S: int) -> float:
+        d, L, V = cfg.n_embd, cfg.n_layer, cfg.vocab_size
         T = B * S
-        per_layer = 2.0 * T * d * (3 * d + d + 4 * d + 4 * d) + 4.0 * B * self.cfg.n_head * S * S * self.head_dim * 0.5
+        per_layer = 2.0 * T * d * (3 * d + d + 4 * d + 4 * d) + 4.0 * B * S * S * d * 0.5
         return L * per_layer + 2.0 * T * d * V
 
 
