@@ -29,21 +29,28 @@ constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int THREADS = 192;      // TMA warp, MMA warp, four epilogue warps
 constexpr int MAX_THREADS = 320;  // ... or eight epilogue warps: two per TMEM lane quarter, each taking half the columns
-// Eight pay when the epilogue is the longer stage of a tile: short K, or an activation to evaluate
-// (measured: 8192 x 2304 x 768 691 -> 799 TFLOP/s, with GELU 508 -> 683); very wide outputs and long K
-// run a little faster with four.
-static inline int launch_threads(int64_t M, int64_t N, int64_t K, int act) {
+// Eight pay when the epilogue is the longer stage of a tile or sits in the tail: short K, an activation
+// to evaluate, or so few tiles that the last epilogue is exposed (measured with the TMA-store epilogue:
+// 8192 x 2304 x 768 808 -> 1034 TFLOP/s, with GELU 562 -> 766, 8192 x 768 x 3072 900 -> 971); long-K
+// products with many tiles run 1-2 % faster with four.
+static inline int launch_threads(int64_t M, int64_t N, int64_t K, int act, int sm_count) {
   const int64_t forced = option("gemm_epi_warps", 0);
   if (forced) return forced == 8 ? MAX_THREADS : THREADS;
-  return (act != 0 || (K <= 1024 && M * N <= (1ll << 26))) ? MAX_THREADS : THREADS;
+  const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  return (act != 0 || K <= 1536 || tiles <= sm_count) ? MAX_THREADS : THREADS;
 }
+
+// Output staging for the TMA-store epilogue: 32 KiB shared by the epilogue warps, in 4 KiB slots of
+// 32 rows x 128 bytes (two slots per warp with four epilogue warps, one with eight).
+constexpr int STAGING_BYTES = 32 * 1024;
+constexpr int SLOT_BYTES = 4096;
 
 template <int BN, int STAGES>
 struct Cfg {
   static constexpr int B_BYTES = BK * BN * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES + 1024;
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -145,6 +152,154 @@ __device__ __forceinline__ void apply_bias_act(uint32_t (&acc)[32], const EpiArg
   }
 }
 
+// TMA-store epilogue.  A warp converts its 32 accumulator rows to the output type, writes them into a
+// 4 KiB slot of shared memory in the 128-byte-swizzle layout (row r, 16-byte chunk c at chunk c ^ (r & 7):
+// conflict-free for one row per lane) and lane 0 issues one tiled bulk store for the slot: 64 fp16 or
+// 32 fp32 columns x 32 rows.  The store engine writes whole 128-byte row segments and clips at the
+// matrix edges, where the direct path has each lane write 16-byte pieces of its own row.
+template <typename OutT>
+struct StoreStager {
+  uint32_t buf0;            // shared address of this warp's first slot (1024-aligned)
+  uint8_t *gen0;            // the same slot through a generic pointer
+  int nbuf;                 // slots this warp owns: 1 or 2
+  int n;                    // stores issued so far
+  const CUtensorMap *tm;
+  int lane;
+
+  __device__ __forceinline__ uint32_t off() const { return (uint32_t)(n & (nbuf - 1)) * SLOT_BYTES; }
+  // the bulk store that last used the slot has finished reading it
+  __device__ __forceinline__ void acquire() {
+    if (lane == 0) {
+      if (nbuf == 2) tc::bulk_wait_group_read<1>();
+      else tc::bulk_wait_group_read<0>();
+    }
+    __syncwarp();
+  }
+  __device__ __forceinline__ void release(int x, int y) {
+    tc::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tc::tma_store_2d(tm, buf0 + off(), x, y);
+      tc::bulk_commit_group();
+    }
+    ++n;
+  }
+  __device__ __forceinline__ void drain() {
+    if (lane == 0) tc::bulk_wait_group_read<0>();
+    __syncwarp();
+  }
+  // 32 accumulator columns [col0, col0 + 32) of this lane's row; rrow: residual row or null
+  __device__ __forceinline__ void put32(const uint32_t (&acc)[32], const __half *rrow, int r_vec, int col0, int row0w,
+                                        int N);
+};
+
+template <>
+__device__ __forceinline__ void StoreStager<__half>::put32(const uint32_t (&acc)[32], const __half *rrow, int r_vec,
+                                                           int col0, int row0w, int N) {
+  const int h = (col0 >> 5) & 1;  // which half of the 64-column slot
+  if (h == 0) acquire();
+  uint8_t *row = gen0 + off() + lane * 128;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int c = col0 + g * 8;
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(acc[g * 8 + e]);
+    if (rrow) {
+      if (r_vec && c + 8 <= N) {
+        Vec16<__half> r;
+        r.raw = *reinterpret_cast<const uint4 *>(rrow + c);
+        float rf[8];
+        r.unpack(rf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += rf[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (c + e < N) f[e] += __half2float(rrow[c + e]);
+      }
+    }
+    Vec16<__half> o;
+    o.pack(f);
+    *reinterpret_cast<uint4 *>(row + (((h * 4 + g) ^ (lane & 7)) << 4)) = o.raw;
+  }
+  if (h == 1) release(col0 - 32, row0w);
+}
+
+template <>
+__device__ __forceinline__ void StoreStager<float>::put32(const uint32_t (&acc)[32], const __half *rrow, int r_vec,
+                                                          int col0, int row0w, int N) {
+  (void)r_vec;
+  acquire();
+  uint8_t *row = gen0 + off() + lane * 128;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const int c = col0 + g * 4;
+    float f[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) f[e] = __uint_as_float(acc[g * 4 + e]);
+    if (rrow) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (c + e < N) f[e] += __half2float(rrow[c + e]);
+    }
+    *reinterpret_cast<float4 *>(row + ((g ^ (lane & 7)) << 4)) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+  release(col0, row0w);
+}
+
+template <typename OutT>
+__device__ __forceinline__ StoreStager<OutT> make_stager(uint8_t *staging, uint32_t staging_addr, const CUtensorMap *tm,
+                                                         int warp, int lane) {
+  const int n_epi = (blockDim.x >> 5) - 2;           // 4 or 8 epilogue warps
+  const int per_warp = STAGING_BYTES / n_epi;        // 8 KiB or 4 KiB
+  StoreStager<OutT> st;
+  st.buf0 = staging_addr + (uint32_t)((warp - 2) * per_warp);
+  st.gen0 = staging + (warp - 2) * per_warp;
+  st.nbuf = per_warp / SLOT_BYTES;
+  st.n = 0;
+  st.tm = tm;
+  st.lane = lane;
+  return st;
+}
+
+// Drains this warp's share of one accumulator buffer.  taddr: TMEM address of the warp's lane quarter at
+// the buffer's first column; `width` output columns starting at col_base.  With two warps per lane
+// quarter (halves == 2) the columns are split in units of 64 so that a slot is always filled by one warp.
+template <typename OutT, int EPI, int BN>
+__device__ __forceinline__ void drain_accumulator(uint32_t taddr, int width, int col_base, int row, int row0w, int M,
+                                                  int N, OutT *C, int64_t ldc, const __half *R, int64_t ldr, int vec_ok,
+                                                  const EpiArgs &epi, int halves, int half, StoreStager<OutT> &st,
+                                                  int use_tma, int r_vec) {
+  const int units = (EPI == 1 ? BN / 2 : width) / 64;
+  const int mid = halves == 1 ? units : (units + 1) / 2;
+  const int ubeg = half == 0 ? 0 : mid, uend = half == 0 ? mid : units;
+  OutT *crow = C + (int64_t)row * ldc;
+  const __half *rrow = (R && row < M) ? R + (int64_t)row * ldr : nullptr;
+#pragma unroll 1
+  for (int c = 2 * ubeg; c < 2 * uend; ++c) {
+    uint32_t v[32];
+    if constexpr (EPI == 1) {
+      uint32_t u[32];
+      tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
+      tc::tmem_ld_32x32(taddr + (uint32_t)(BN / 2 + c * 32), u);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const float gv = __uint_as_float(v[e]);
+        v[e] = __float_as_uint(__fdividef(gv, 1.0f + __expf(-gv)) * __uint_as_float(u[e]));
+      }
+    } else {
+      tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
+      tc::tmem_ld_wait();
+    }
+    const int col0 = col_base + c * 32;
+    if constexpr (EPI == 2) apply_bias_act(v, epi, col0, N);
+    if (use_tma) st.put32(v, rrow, r_vec, col0, row0w, N);
+    else if (row < M && col0 < N) store_row_chunk<OutT>(crow, rrow, v, col0, N, vec_ok != 0);
+  }
+}
+
 // EPI == 1 (SwiGLU, BN = 256, fp16 out): B is a [K, 2*N] gate|up matrix; a tile's B operand is made
 // of 128 gate columns [col0, col0+128) and the 128 up columns [N+col0, N+col0+128), so accumulator
 // columns c and 128+c belong to output column col0+c and the epilogue writes silu(gate) * up.
@@ -155,7 +310,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
                int64_t ldr, int tiles_m, int tiles_n, int vec_ok, uint32_t b_lbo, uint32_t b_sbo,
-               int full_items, int split, const EpiArgs epi) {
+               int full_items, int split, const EpiArgs epi, const __grid_constant__ CUtensorMap tmC, int use_tma,
+               int r_vec) {
   using cfg = Cfg<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
@@ -163,8 +319,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint8_t *smem = smem_raw + pad;
   const uint32_t smem_addr = raw_addr + pad;
 
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * cfg::STAGE_BYTES);
-  const uint32_t bar0 = smem_addr + STAGES * cfg::STAGE_BYTES;
+  uint8_t *staging = smem + STAGES * cfg::STAGE_BYTES;
+  const uint32_t staging_addr = smem_addr + STAGES * cfg::STAGE_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(staging + STAGING_BYTES);
+  const uint32_t bar0 = staging_addr + STAGING_BYTES;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
@@ -291,49 +449,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------ epilogue (warps 2..5 or 2..9)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     const int halves = ((blockDim.x >> 5) - 2) >> 2, half = (warp - 2) >> 2;  // column share of this warp
+    StoreStager<OutT> st = make_stager<OutT>(staging, staging_addr, &tmC, warp, lane);
     int t = 0;
     for (int item = blockIdx.x; item < num_items; item += gridDim.x, ++t) {
       const Item w = item_of(item);
-      const int tm = w.tm;
       const int acc = t & 1;
       if (!tc::mbar_wait(tfull_bar(acc), (uint32_t)(t >> 1) & 1u, abort_flag)) break;
       tc::tc_fence_after();
-      const int row = tm * BM + q * 32 + lane;
+      const int row0w = w.tm * BM + q * 32;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-      OutT *crow = C + (int64_t)row * ldc;
-      const __half *rrow = R ? R + (int64_t)row * ldr : nullptr;
-      if constexpr (EPI == 1) {
-        const int nch = BN / 64 / halves;
-#pragma unroll 1
-        for (int c = half * nch; c < (half + 1) * nch; ++c) {
-          uint32_t g[32], u[32];
-          tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), g);
-          tc::tmem_ld_32x32(taddr + (uint32_t)(BN / 2 + c * 32), u);
-          tc::tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float gv = __uint_as_float(g[e]);
-            g[e] = __float_as_uint(__fdividef(gv, 1.0f + __expf(-gv)) * __uint_as_float(u[e]));
-          }
-          const int col0 = w.col0 + c * 32;
-          if (row < M && col0 < N) store_row_chunk<OutT>(crow, nullptr, g, col0, N, vec_ok != 0);
-        }
-      } else {
-        const int nch = w.width / 32 / halves;  // widths are multiples of 64
-#pragma unroll 1
-        for (int c = half * nch; c < (half + 1) * nch; ++c) {
-          uint32_t v[32];
-          tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
-          tc::tmem_ld_wait();
-          const int col0 = w.col0 + c * 32;
-          if constexpr (EPI == 2) apply_bias_act(v, epi, col0, N);
-          if (row < M && col0 < N) store_row_chunk<OutT>(crow, rrow, v, col0, N, vec_ok != 0);
-        }
-      }
+      drain_accumulator<OutT, EPI, BN>(taddr, w.width, w.col0, row0w + lane, row0w, M, N, C, ldc, R, ldr, vec_ok, epi,
+                                       halves, half, st, use_tma, r_vec);
       tc::tc_fence_before();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(tempty_bar(acc));
     }
+    if (use_tma) st.drain();  // shared memory stays allocated until the last store has read it
   }
 
   // ------------------------------------------------------------ teardown
@@ -390,7 +521,7 @@ constexpr int STAGES = 6;
 constexpr int BN = 256;
 constexpr int B_HALF_BYTES = BK * 128 * 2;             // this CTA's 128 columns of the B tile: 16 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_HALF_BYTES;    // 32 KiB
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
 constexpr int TMEM_COLS = 512;
 }  // namespace pair
 
@@ -398,15 +529,18 @@ template <typename OutT, int EPI, bool BT = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MAX_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
-                    int64_t ldr, int tiles_m, int tiles_n, int vec_ok, const EpiArgs epi) {
+                    int64_t ldr, int tiles_m, int tiles_n, int vec_ok, const EpiArgs epi,
+                    const __grid_constant__ CUtensorMap tmC, int use_tma, int r_vec) {
   using namespace pair;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
   uint8_t *smem = smem_raw + pad;
   const uint32_t smem_addr = raw_addr + pad;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
-  const uint32_t bar0 = smem_addr + STAGES * STAGE_BYTES;
+  uint8_t *staging = smem + STAGES * STAGE_BYTES;
+  const uint32_t staging_addr = smem_addr + STAGES * STAGE_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(staging + STAGING_BYTES);
+  const uint32_t bar0 = staging_addr + STAGING_BYTES;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };                   // used in the leader only
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };       // one per CTA
   auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };   // one per CTA
@@ -509,48 +643,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ------------------------------------------------------------ epilogue (warps 2..5 or 2..9, both CTAs)
     const int q = warp & 3;
     const int halves = ((blockDim.x >> 5) - 2) >> 2, half = (warp - 2) >> 2;
+    StoreStager<OutT> st = make_stager<OutT>(staging, staging_addr, &tmC, warp, lane);
     int t = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++t) {
       const int tm = tile % tiles_m, col_base = (tile / tiles_m) * OUT_COLS;
       const int acc = t & 1;
       if (!tc::mbar_wait(tfull_bar(acc), (uint32_t)(t >> 1) & 1u, abort_flag)) break;
       tc::tc_fence_after();
-      const int row = tm * 256 + (int)rank * BM + q * 32 + lane;
+      const int row0w = tm * 256 + (int)rank * BM + q * 32;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-      OutT *crow = C + (int64_t)row * ldc;
-      const __half *rrow = R ? R + (int64_t)row * ldr : nullptr;
-      if constexpr (EPI == 1) {
-        const int nch = BN / 64 / halves;
-#pragma unroll 1
-        for (int c = half * nch; c < (half + 1) * nch; ++c) {
-          uint32_t g[32], u[32];
-          tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), g);
-          tc::tmem_ld_32x32(taddr + (uint32_t)(BN / 2 + c * 32), u);
-          tc::tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float gv = __uint_as_float(g[e]);
-            g[e] = __float_as_uint(__fdividef(gv, 1.0f + __expf(-gv)) * __uint_as_float(u[e]));
-          }
-          const int col0 = col_base + c * 32;
-          if (row < M && col0 < N) store_row_chunk<OutT>(crow, nullptr, g, col0, N, vec_ok != 0);
-        }
-      } else {
-        const int nch = BN / 32 / halves;
-#pragma unroll 1
-        for (int c = half * nch; c < (half + 1) * nch; ++c) {
-          uint32_t v[32];
-          tc::tmem_ld_32x32(taddr + (uint32_t)(c * 32), v);
-          tc::tmem_ld_wait();
-          const int col0 = col_base + c * 32;
-          if constexpr (EPI == 2) apply_bias_act(v, epi, col0, N);
-          if (row < M && col0 < N) store_row_chunk<OutT>(crow, rrow, v, col0, N, vec_ok != 0);
-        }
-      }
+      drain_accumulator<OutT, EPI, BN>(taddr, BN, col_base, row0w + lane, row0w, M, N, C, ldc, R, ldr, vec_ok, epi, halves,
+                                       half, st, use_tma, r_vec);
       tc::tc_fence_before();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_rank(tempty_bar(acc), 0));
     }
+    if (use_tma) st.drain();
   }
 
   // ------------------------------------------------------------ teardown
@@ -566,8 +674,38 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_status, (int)HEXB_ERR_TIMEOUT);
 }
 
+// Tensor map of the output for the TMA-store epilogue (use == 0: the lanes store their rows directly).
+struct StoreMap {
+  CUtensorMap tm;
+  int use;
+  int r_vec;  // the residual rows can be read with 16-byte loads
+};
+
+template <typename OutT>
+static StoreMap make_store_map(OutT *C, const __half *R, int64_t M, int64_t N, int64_t ldc, int64_t ldr,
+                               const CUtensorMap &fallback) {
+  StoreMap sm;
+  sm.tm = fallback;
+  sm.use = 0;
+  sm.r_vec = R && aligned16(R) && ldr % 8 == 0;
+  if (!option("gemm_tma_store", 1) || !aligned16(C) || (ldc * (int64_t)sizeof(OutT)) % 16) return sm;
+  const uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+  int rc;
+  if (sizeof(OutT) == 2) {
+    const uint64_t strides[1] = {(uint64_t)ldc * 2};
+    const uint32_t box[2] = {64, 32};
+    rc = encode_tmap_f16_sw128(&sm.tm, C, 2, dims, strides, box);
+  } else {
+    const uint32_t box[2] = {32, 32};
+    rc = encode_tmap_f32_sw128_2d(&sm.tm, C, dims, (uint64_t)ldc * 4, box);
+  }
+  if (rc == HEXB_OK) sm.use = 1;
+  else sm.tm = fallback;
+  return sm;
+}
+
 template <typename OutT, int EPI, bool BT = false>
-static int launch_tc_pair(const EpiArgs &epi, const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M, int N,
+static int launch_tc_pair(const EpiArgs &epi, const StoreMap &sm, const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M, int N,
                           int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count, cudaStream_t st) {
   static bool attr_done[64] = {};
   int dev = 0;
@@ -581,13 +719,13 @@ static int launch_tc_pair(const EpiArgs &epi, const CUtensorMap &tmA, const CUte
   const int tiles_m = (M + 255) / 256, tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
   const int tiles = tiles_m * tiles_n;
   const int clusters = tiles < sm_count / 2 ? tiles : sm_count / 2;
-  kern<<<2 * clusters, launch_threads(M, N, K, EPI == 1 ? 1 : epi.act), pair::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok,
-                                                        epi);
+  kern<<<2 * clusters, launch_threads(M, N, K, EPI == 1 ? 1 : epi.act, sm_count), pair::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok,
+                                                        epi, sm.tm, sm.use, sm.r_vec);
   return check_launch("gemm_tc_pair");
 }
 
 template <int BN, int STAGES, typename OutT, int EPI = 0, bool BT = false>
-static int launch_tc(const EpiArgs &epi, const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M,
+static int launch_tc(const EpiArgs &epi, const StoreMap &sm, const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M,
                      int N, int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count,
                      cudaStream_t st) {
   using cfg = Cfg<BN, STAGES>;
@@ -613,8 +751,8 @@ static int launch_tc(const EpiArgs &epi, const CUtensorMap &tmA, const CUtensorM
   const int grid = items < sm_count ? items : sm_count;
   const uint32_t lbo = (uint32_t)option("gemm_b_lbo", BK * 128);
   const uint32_t sbo = (uint32_t)option("gemm_b_sbo", 1024);
-  kern<<<grid, launch_threads(M, N, K, EPI == 1 ? 1 : epi.act), cfg::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n,
-                                               vec_ok, lbo, sbo, full_items, split, epi);
+  kern<<<grid, launch_threads(M, N, K, EPI == 1 ? 1 : epi.act, sm_count), cfg::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n,
+                                               vec_ok, lbo, sbo, full_items, split, epi, sm.tm, sm.use, sm.r_vec);
   return check_launch("gemm_tc");
 }
 
@@ -655,6 +793,7 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
   }
   constexpr int EV = 16 / (int)sizeof(OutT);
   const int vec_ok = (ldc % EV == 0) && aligned16(C) && (!R || (sizeof(OutT) == 2 && aligned16(R)));
+  const StoreMap sm = make_store_map<OutT>(C, R, M, N, ldc, ldr, tmA);
   const int tiles_m = (int)((M + BM - 1) / BM);
   int bn = option("gemm_bn", 0);
   if (bn != 64 && bn != 128 && bn != 256) {
@@ -665,15 +804,15 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
   // CTA-pair kernel for problems with at least one 256 x 256 tile per pair of SMs
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
   if (option("gemm_bn", 0) == 0 && option("gemm_pair", 1) && pair_tiles >= di.sm_count / 2)
-    return launch_tc_pair<OutT, EPI, BT>(epi, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+    return launch_tc_pair<OutT, EPI, BT>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
   if (BT && bn == 64) bn = 128;  // the transposed form loads Bt in 128-row boxes
   switch (bn) {
     case 64:
-      return launch_tc<64, 8, OutT, EPI, false>(epi, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<64, 8, OutT, EPI, false>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
     case 128:
-      return launch_tc<128, 6, OutT, EPI, BT>(epi, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<128, 6, OutT, EPI, BT>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
     default:
-      return launch_tc<256, 4, OutT, EPI, BT>(epi, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<256, 4, OutT, EPI, BT>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
   }
 }
 
@@ -776,10 +915,11 @@ extern "C" int hexb_matmul_swiglu_f16(const void *A, const void *B_gate_up, void
     if (int s = encode_tmap_f16_sw128(&tmB, B_gate_up, 2, dims, strides, box)) return s;
   }
   const int vec_ok = (ldo % 8 == 0) && aligned16(out);
+  const gemm::StoreMap sm = gemm::make_store_map<__half>((__half *)out, nullptr, M, F, ldo, ldo, tmA);
   if (option("gemm_pair", 1) && ((M + 255) / 256) * ((F + 127) / 128) >= di.sm_count / 2)
-    return launch_tc_pair<__half, 1>(gemm::EpiArgs{nullptr, 0}, tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
+    return launch_tc_pair<__half, 1>(gemm::EpiArgs{nullptr, 0}, sm, tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
                                      di.sm_count, (cudaStream_t)stream);
-  return launch_tc<256, 4, __half, 1>(gemm::EpiArgs{nullptr, 0}, tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
+  return launch_tc<256, 4, __half, 1>(gemm::EpiArgs{nullptr, 0}, sm, tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
                                       di.sm_count, (cudaStream_t)stream);
 }
 

@@ -95,6 +95,20 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, int 
       : "memory");
 }
 
+// Tiled store shared -> global (bulk async-group completion).  The box is clipped at the tensor's
+// extents, so ragged edges need no special handling; x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_store_2d(const void *tmap, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tmap), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once at most N of this thread's bulk groups still have to READ their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
 // ------------------------------------------------------------------ TMEM
 // Whole-warp calls (.sync.aligned).  ncols: power of two, 32..512.
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -285,6 +299,8 @@ __device__ __forceinline__ void tmem_st_wait() {
 // Encodes a tiled tensor map (128-byte swizzle, fp16) through the driver entry point fetched with
 // cudaGetDriverEntryPoint, so the library links against the CUDA runtime only.
 // dims/strides: innermost first; strides_bytes[i] is the byte stride of dimension i+1.
+int encode_tmap_f32_sw128_2d(CUtensorMap *out, const void *base, const uint64_t *dims, uint64_t row_stride_bytes,
+                             const uint32_t *box);
 int encode_tmap_f16_sw128(CUtensorMap *out, const void *base, int rank, const uint64_t *dims,
                           const uint64_t *strides_bytes, const uint32_t *box);
 

@@ -57,6 +57,28 @@ int encode_tmap_f16_sw128(CUtensorMap *out, const void *base, int rank, const ui
   return HEXB_OK;
 }
 
+// Same for a 2-D fp32 tensor (dims and box in elements; the box's inner extent is 32 floats = 128 bytes).
+int encode_tmap_f32_sw128_2d(CUtensorMap *out, const void *base, const uint64_t *dims, uint64_t row_stride_bytes,
+                             const uint32_t *box) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_cuda_error(cudaErrorNotSupported, "cuTensorMapEncodeTiled entry point");
+    return HEXB_ERR_CUDA;
+  }
+  if (!aligned16(base) || row_stride_bytes % 16) return HEXB_ERR_MISALIGNED;
+  if (dims[0] == 0 || dims[1] == 0) return HEXB_ERR_BAD_ARG;
+  cuuint64_t gd[2] = {dims[0], dims[1]}, gs[1] = {row_stride_bytes};
+  cuuint32_t bx[2] = {box[0], box[1]}, es[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), gd, gs, bx, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+    return HEXB_ERR_CUDA;
+  }
+  return HEXB_OK;
+}
+
 int gemm_device_status_fetch_and_clear(int *out);
 int attn_device_status_fetch_and_clear(int *out);
 int norm_device_status_fetch_and_clear(int *out);
