@@ -390,9 +390,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // scores ready when they finish a block and the tensor pipe works through Q.K^T / P.V while they
 // exponentiate.  P_j is written over the first 32 columns of S buffer j%2; Q.K_{j+2}^T, which
 // overwrites it, is issued after P_j.V_j (the tensor pipe retires in issue order).
-template <int HD>
+// BN_ = 128 (no mask; option attn_kernel = 5): key blocks twice as wide, so Q is read from shared memory
+// once per 128 keys instead of twice; the two score buffers then take 256 TMEM columns and O sits at
+// 256: all 512 columns and 160 KiB of shared memory, i.e. one CTA per SM, whose softmax threads hold
+// the 128 scores of a row in registers.  Measured slower than two CTAs per SM with 64-key blocks
+// ([4,32,4096,128]: 947 vs 1086 TFLOP/s, causal 834 vs 980): with four softmax warps per SM the
+// exponentials, not the shared-memory reads, set the pace.  A variant with two query tiles per CTA
+// taking turns on the tensor pipe (eight softmax warps, 128-key blocks, one score buffer per tile)
+// measured 1070 / 872: the same pace as the default, bounded the same way.
+template <int HD, int BN_ = 64>
 struct Cfg2 {
-  static constexpr int BN = 64;                       // keys per block
+  static constexpr int BN = BN_;                      // keys per block
   static constexpr int CHUNKS = HD / 64;
   static constexpr int Q_BYTES = 128 * HD * 2;
   static constexpr int Q_CHUNK = 128 * 128;           // 128 rows x 128 bytes
@@ -408,19 +416,20 @@ struct Cfg2 {
   static constexpr int MASK_STAGE = 32 * 128;
   static constexpr int MASK_BYTES = 4 * MASK_STAGE;
   static constexpr int SMEM_BYTES_MASK = Q_BYTES + 4 * KV_BYTES + MASK_BYTES + NBAR * 8 + 16 + 160;
-  static constexpr int TMEM_COLS = 256;               // S0 [0,64), S1 [64,128), O [128,128+HD); P_b over S_b[0,32)
-  static constexpr int O_COL = 128;
+  static constexpr int TMEM_COLS = BN == 64 ? 256 : 512;   // S0 [0,BN), S1 [BN,2BN), O [2BN,2BN+HD); P_b over S_b[0,BN/2)
+  static constexpr int O_COL = 2 * BN;
 };
 
 // MASK: an additive mask tile is read by the softmax warps and the scores are formed in the base-2
 // domain as s * scale * log2(e) + mask * log2(e) before the running maximum is taken.
-template <int HD, bool MASK>
-__global__ void __launch_bounds__(THREADS, 2)
+template <int HD, bool MASK, int BN_ = 64>
+__global__ void __launch_bounds__(THREADS, BN_ == 64 ? 2 : 1)
 attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmM,
                     const Params p) {
-  using cfg = Cfg2<HD>;
+  using cfg = Cfg2<HD, BN_>;
   constexpr int BN = cfg::BN;
+  static_assert(!MASK || BN == 64, "the masked variant stages 64-key mask tiles");
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
@@ -458,9 +467,9 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (p.causal) return t == 0 ? p.num_q_tiles - 1 - q_rank : q_rank;
     return q_rank * p.tiles_per_cta + t;
   };
-  // causal: keys 0 .. m0+127 -> 2*(q_tile+1) blocks of 64
+  // causal: keys 0 .. m0+127 -> (q_tile+1) * 128 / BN blocks
   auto nkv_of = [&](int q_tile) {
-    const int need = 2 * (q_tile + 1);
+    const int need = (BLOCK_M / BN) * (q_tile + 1);
     return (p.causal && need < kv_blocks) ? need : kv_blocks;
   };
 
@@ -934,14 +943,16 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   using cfg = Cfg<HD>;
   // 2: 64-key blocks, two score buffers; 1: 128-key blocks (plain calls only)
   const bool plain = !x.mask && !x.out_f32 && x.n_kv == N;
-  const bool two_buffers = !plain || option("attn_kernel", 2) == 2;
+  const int which = (int)option("attn_kernel", 2);
+  const bool two_buffers = !plain || which != 1;
+  const bool wide = two_buffers && !x.mask && which == 5;  // 128-key blocks, one CTA per SM
   CUtensorMap tm[4];
   const __half *base[3] = {Q, K, V};
   for (int i = 0; i < 3; ++i) {
     const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)(i == 0 ? N : x.n_kv), (uint64_t)H, (uint64_t)Z};
     const uint64_t strides[3] = {(uint64_t)s[3 * i + 2] * 2, (uint64_t)s[3 * i + 1] * 2,
                                  (uint64_t)s[3 * i + 0] * 2};
-    const uint32_t box[4] = {64, (i > 0 && two_buffers) ? 64u : 128u, 1, 1};
+    const uint32_t box[4] = {64, (i > 0 && two_buffers && !wide) ? 64u : 128u, 1, 1};  // rows per K/V load
     if (int e = encode_tmap_f16_sw128(&tm[i], base[i], 4, dims, strides, box)) return e;
   }
   static bool attr_done[64] = {};
@@ -953,6 +964,8 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
                                       Cfg2<HD>::SMEM_BYTES));
     HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg2<HD>::SMEM_BYTES_MASK));
+    HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg2<HD, 128>::SMEM_BYTES));
     attr_done[dev & 63] = true;
   }
   Params p;
@@ -1002,7 +1015,10 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   p.ctas_per_bh = p.num_q_tiles / p.tiles_per_cta;
   const int64_t ctas = (int64_t)p.ctas_per_bh * Z * H;
   if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
-  if (two_buffers && x.mask)
+  if (wide)
+    attn_fwd_tc2_kernel<HD, false, 128><<<(unsigned)ctas, THREADS, Cfg2<HD, 128>::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2],
+                                                                                                  tm[3], p);
+  else if (two_buffers && x.mask)
     attn_fwd_tc2_kernel<HD, true><<<(unsigned)ctas, THREADS, Cfg2<HD>::SMEM_BYTES_MASK, st>>>(tm[0], tm[1], tm[2],
                                                                                              tm[3], p);
   else if (two_buffers)

@@ -650,3 +650,22 @@ def test_attention_masked_f32_and_odd_head_dim(dev):
     # fp16 tensors of the same odd shape take the CUDA-core path too, with an fp32 result
     ops.attention_ex(q.half().to(dev), k.half().to(dev), v.half().to(dev), out, mask=mask.half().to(dev))
     assert O.max_rel_err(out.cpu(), _sdpa_ref(q.half(), k.half(), v.half(), mask.half(), 1.0 / math.sqrt(D))) < REL_F16
+
+
+@pytest.mark.parametrize("which", [1, 5])
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_selectable_kernels_agree_with_default(dev, which, causal):
+    """The 128-key single-buffer kernel (1) and the 128-key two-buffer kernel (5) stay selectable; they
+    must give the default kernel's result to rounding on full, ragged and odd-tile-count shapes."""
+    for Z, H, N, D in [(1, 2, 512, 128), (2, 1, 300, 64), (1, 1, 640, 128)]:
+        g = torch.Generator().manual_seed(N + D + which)
+        q, k, v = (torch.randn(Z, H, N, D, generator=g).half().to(dev) for _ in range(3))
+        a, b = torch.empty_like(q), torch.empty_like(q)
+        ops.attention(q, k, v, a, causal=causal)
+        hexb200.set_option("attn_kernel", which)
+        try:
+            ops.attention(q, k, v, b, causal=causal)
+        finally:
+            hexb200.set_option("attn_kernel", 2)
+        assert hexb200.device_status() == 0
+        assert O.max_rel_err(b.cpu(), a.cpu()) < 2e-3
