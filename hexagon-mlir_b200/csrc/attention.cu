@@ -74,6 +74,24 @@ __device__ __forceinline__ float ex2_poly(float x) {
 // bound by instruction issue before the special-function unit, so the offload stays off.
 constexpr int kPolyEvery = 0;  // one exponential in kPolyEvery goes through ex2_poly (0 = none)
 
+// Two fp32 lanes per instruction (sm_100 packed arithmetic): halves the issue slots of the scale-and-
+// shift and of the row-sum in the softmax loop, which is bound by instruction issue.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(reinterpret_cast<unsigned long long &>(d))
+      : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)),
+        "l"(reinterpret_cast<unsigned long long &>(c)));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<unsigned long long &>(d))
+      : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)));
+  return d;
+}
+
 // {lo, hi} -> packed fp16 pair (lo in bits 0..15)
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   uint32_t r;
@@ -741,21 +759,25 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // a row whose keys so far are all masked to -inf keeps m_ref = -inf: its weights must come out 0, not NaN
         const float neg_m = (MASK && m_ref == -INFINITY) ? 0.f : -m_ref;
         const float mul = MASK ? 1.0f : p.scale_log2;
-        float l0 = 0.f, l1 = 0.f;
+        const float2 mul2 = make_float2(mul, mul), neg_m2 = make_float2(neg_m, neg_m);
+        float2 lacc0 = make_float2(0.f, 0.f), lacc1 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + e]), mul, neg_m));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[c * 32 + e + 1]), mul, neg_m));
-            l0 += p0;
-            l1 += p1;
-            pk[e >> 1] = pack_f16x2(p0, p1);
+          for (int e = 0; e < 32; e += 4) {
+            const float2 xa = fma2(make_float2(__uint_as_float(sv[c * 32 + e]), __uint_as_float(sv[c * 32 + e + 1])), mul2, neg_m2);
+            const float2 xb = fma2(make_float2(__uint_as_float(sv[c * 32 + e + 2]), __uint_as_float(sv[c * 32 + e + 3])), mul2, neg_m2);
+            const float2 pa = make_float2(ex2_approx(xa.x), ex2_approx(xa.y));
+            const float2 pb = make_float2(ex2_approx(xb.x), ex2_approx(xb.y));
+            lacc0 = add2(lacc0, pa);
+            lacc1 = add2(lacc1, pb);
+            pk[e >> 1] = pack_f16x2(pa.x, pa.y);
+            pk[(e >> 1) + 1] = pack_f16x2(pb.x, pb.y);
           }
           tc::tmem_st_32x16(tP + lane_off + (uint32_t)(c * 16), pk);
         }
-        l += l0 + l1;
+        l += (lacc0.x + lacc0.y) + (lacc1.x + lacc1.y);
         HEXB_PROF(4)  // exp, pack, TMEM store issue
         tc::tmem_st_wait();
         tc::tc_fence_before();
