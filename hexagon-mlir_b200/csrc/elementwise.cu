@@ -8,7 +8,7 @@
 
 namespace hexb {
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }  // 2 ulp
 
 template <typename T>
 __global__ void __launch_bounds__(256) silu_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t n,
