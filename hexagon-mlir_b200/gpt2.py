@@ -83,6 +83,7 @@ class GPT2Runner:
         if missing:
             raise KeyError(f"GPT2Runner: missing weights {missing[:4]}{'...' if len(missing) > 4 else ''}")
         self._bufs = {}
+        self._graphs = {}
 
     def launches(self) -> int:
         """Kernel launches of one forward pass (embedding + blocks + final norm + LM head)."""
@@ -102,19 +103,41 @@ class GPT2Runner:
             }
         return self._bufs[key]
 
-    def forward(self, input_ids: torch.Tensor, logits_dtype=torch.float32) -> torch.Tensor:
+    def forward(self, input_ids: torch.Tensor, logits_dtype=torch.float32, graph: bool = False) -> torch.Tensor:
         """input_ids: int64 [batch, seq] on the runner's device.  Returns logits [batch, seq, vocab]
-        (a buffer owned by the runner, overwritten by the next call with the same shape)."""
-        cfg, w = self.cfg, self.w
+        (a buffer owned by the runner, overwritten by the next call with the same shape).
+
+        graph=True replays the 17 launches as one CUDA graph captured on the first call with this
+        (batch, seq, logits dtype): for short prompts the launches, not the kernels, set the latency."""
+        cfg = self.cfg
         if input_ids.dim() != 2 or input_ids.dtype != torch.int64 or input_ids.device != self.device:
             raise ValueError("GPT2Runner: int64 [batch, seq] ids on the runner's device expected")
         B, S = input_ids.shape
         if S > cfg.n_positions:
             raise ValueError("GPT2Runner: sequence longer than n_positions")
+        if not graph:
+            return self._forward(input_ids.contiguous(), logits_dtype)
+        key = (B, S, logits_dtype)
+        if key not in self._graphs:
+            static_ids = input_ids.clone()
+            self._forward(static_ids, logits_dtype)          # first call outside capture: one-time set-up
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out = self._forward(static_ids, logits_dtype)
+            self._graphs[key] = (g, static_ids, out)
+        g, static_ids, out = self._graphs[key]
+        static_ids.copy_(input_ids)
+        g.replay()
+        return out
+
+    def _forward(self, input_ids: torch.Tensor, logits_dtype) -> torch.Tensor:
+        cfg, w = self.cfg, self.w
+        B, S = input_ids.shape
         d, H, D = cfg.n_embd, cfg.n_head, self.head_dim
         b = self._buffers(B, S, logits_dtype)
         x, x2 = b["x"], b["x2"]
-        ops.embedding(w["transformer.wte.weight"], w["transformer.wpe.weight"], input_ids.contiguous(), x.view(B, S, d))
+        ops.embedding(w["transformer.wte.weight"], w["transformer.wpe.weight"], input_ids, x.view(B, S, d))
         qkv4 = b["qkv"].view(B, S, 3, H, D)
         q, k, v = (qkv4[:, :, i].permute(0, 2, 1, 3) for i in range(3))      # [B, H, S, D] views of the fused buffer
         att4 = b["att"].view(B, S, H, D).permute(0, 2, 1, 3)

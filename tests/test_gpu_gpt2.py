@@ -114,3 +114,15 @@ def test_gpt2_two_layers_vs_oracle_and_transformers(B, S):
     # fp16 logits on request
     l16 = runner.forward(ids.to(dev), logits_dtype=torch.float16).cpu()
     assert O.max_rel_err(l16[:nb], ref) < REL_F16
+
+
+def test_gpt2_graph_replay_matches_eager():
+    cfg = gpt2.GPT2Config()
+    runner = gpt2.GPT2Runner(cfg, gpt2.random_state_dict(cfg, seed=5), device=dev)
+    g = torch.Generator().manual_seed(0)
+    for _ in range(3):                                    # first call captures, the others replay
+        ids = torch.randint(0, cfg.vocab_size, (1, 128), generator=g).to(dev)
+        a = runner.forward(ids, graph=True).clone()
+        b = runner.forward(ids).clone()
+        assert torch.equal(a, b)
+    assert hexb200.device_status() == 0
