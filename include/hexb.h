@@ -101,7 +101,9 @@ int hexb_matmul_f16_nt(const void *A, const void *Bt, void *C, const void *resid
  * hexb_matmul_f16; act 0 = none, 1 = GELU in the tanh form of gelu_kernel
  * (test/python/triton/test_gelu.py:25-54).  Replaces: the addmm / gelu / add chains of the GPT-2 graph
  * the reference compiles through torch-mlir (test/python/torch-mlir/gpt2lmheadmodel.py:143-169) and
- * lowers op by op to linalg generics around hexkl matmuls. */
+ * lowers op by op to linalg generics around hexkl matmuls.
+ * C may be the residual buffer itself (x = x + A @ W + bias in place: every element is read by the warp
+ * that later stores it); C must not overlap A, W or bias. */
 int hexb_linear_f16(const void *A, const void *W, const void *bias, const void *residual, void *C,
                     int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc,
                     int w_transposed, int act, int out_dtype, void *stream);

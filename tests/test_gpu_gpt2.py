@@ -126,3 +126,19 @@ def test_gpt2_graph_replay_matches_eager():
         b = runner.forward(ids).clone()
         assert torch.equal(a, b)
     assert hexb200.device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 768, 3072), (300, 72, 40)])
+def test_linear_residual_in_place(M, N, K):
+    """x = x + a @ w + bias with the residual and the output in the same buffer: every element is read by
+    the warp that later overwrites it, before its store is issued."""
+    g = torch.Generator().manual_seed(M)
+    a = torch.randn(M, K, generator=g).half()
+    w = (torch.randn(K, N, generator=g) * K ** -0.5).half()
+    bias = torch.randn(N, generator=g).half()
+    x = torch.randn(M, N, generator=g).half()
+    xd = x.to(dev)
+    ops.linear(a.to(dev), w.to(dev), xd, bias=bias.to(dev), residual=xd)
+    ref = x.float() + a.float() @ w.float() + bias.float()
+    assert O.max_rel_err(xd.cpu(), ref) < REL_F16
+    assert hexb200.device_status() == 0
