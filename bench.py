@@ -400,7 +400,7 @@ def cpu_reference_step(name):
     raise KeyError(name)
 
 
-def time_cpu(name, steps, warmup, budget_s=25.0):
+def time_cpu(name, steps, warmup, limit_s=25.0):
     fn, work, sample = cpu_reference_step(name)
     torch.set_num_threads(os.cpu_count() or 1)
     for _ in range(max(1, warmup)):
@@ -411,7 +411,7 @@ def time_cpu(name, steps, warmup, budget_s=25.0):
         t = time.perf_counter()
         fn()
         ts.append(time.perf_counter() - t)
-        if time.perf_counter() - t_all > budget_s:
+        if time.perf_counter() - t_all > limit_s:
             break
     dt = sum(ts) / len(ts)
     return work / dt, dt, len(ts), sample
@@ -631,7 +631,7 @@ def main():
             del w2
             torch.cuda.empty_cache()
         line["workloads"] = extras
-        val, dt, n, sample = time_cpu(args.workload, 8, 2, budget_s=20.0)
+        val, dt, n, sample = time_cpu(args.workload, 8, 2, limit_s=20.0)
         wl_cls = WORKLOADS[args.workload]
         line["cpu_baseline"] = {"value": round(val / scale, 4), "unit": wl_cls.unit, "cores": torch.get_num_threads(),
                                 "kind": "port", "sample": sample, "ms_per_sample": round(dt * 1e3, 3)}

@@ -102,7 +102,7 @@ extern "C" int hexb_decoder_forward_f16(const hexb_decoder_config *cfg, const he
 // ---------------------------------------------------------------------------------------------
 // Allocation-free variant.  The workspace of hexb_decoder_forward_f16 is replaced by a fixed array
 // in the library image, for hosts that cannot call cudaMalloc at this point (all device memory
-// already handed to their own pool, or a latency budget that rules out an allocation).
+// already handed to their own pool, or a latency bound that rules out an allocation).
 //
 // In host code `g_decoder_scratch` is only a handle for the symbol, not a device address: its
 // address is fetched once per device with cudaGetSymbolAddress while that device is current, and

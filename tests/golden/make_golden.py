@@ -1,6 +1,6 @@
 """Generates the golden fixtures in this directory from the reference's own Triton kernels.
 
-Runs only where the reference checkout is present (default /root/reference, or $HEXAGON_MLIR_REF).
+Runs only where a checkout of the reference is present (its location: $HEXAGON_MLIR_REF).
 The reference's test modules are imported unmodified with
 
   * TRITON_INTERPRET=1, so the @triton.jit kernels execute in Triton's NumPy interpreter on CPU,

@@ -39,7 +39,7 @@ def test_split_options_warns_on_option_like_typos_and_rejects_unknowns():
 
 
 def test_option_field_list_matches_the_reference_dataclass():
-    ref = "/root/reference/qcom_hexagon_backend/backend/hexagon_options.py"
+    ref = os.path.join(os.environ.get("HEXAGON_MLIR_REF", "/root/reference"), "qcom_hexagon_backend/backend/hexagon_options.py")
     if not os.path.exists(ref):
         pytest.skip("reference checkout not present")
     import re

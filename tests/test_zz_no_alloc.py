@@ -1,7 +1,7 @@
 """GPU: the allocation-free decoder entry point (hexb_decoder_forward_f16_noalloc).
 
 Some hosts cannot call cudaMalloc when they need a forward pass: they gave all device memory to
-their own pool at start-up, or they run a serving loop whose latency budget has no room for an
+their own pool at start-up, or they run a serving loop whose latency bound leaves no room for an
 allocation.  For them the library carries its intermediate activations in a fixed 64 MiB array
 inside the library image.  This test calls that entry point through the C ABI twice in a row with
 different inputs (the array is shared and keeps the first call's contents, so the second call shows
