@@ -218,3 +218,32 @@ def test_test_info_block():
     assert (back.name, back.perf, back.units, back.result) == ("softmax_kernel", 12.5, "us", "Pass")
     with pytest.raises(ValueError):
         report.TestReport("x", 1.0, "us", "Maybe")
+
+
+def test_gpt2_host_helpers():
+    """The parts of the GPT-2 runner that need no GPU: weight naming, FLOP count, the acceptance rule."""
+    import torch
+    from hexb200 import gpt2
+
+    cfg = gpt2.GPT2Config(n_layer=2, n_embd=64, n_head=4, n_positions=16, vocab_size=50)
+    sd = gpt2.random_state_dict(cfg, seed=0)
+    assert sd["transformer.h.1.attn.c_attn.weight"].shape == (64, 192)          # Conv1D: [in, out]
+    assert sd["transformer.h.0.mlp.c_proj.weight"].shape == (256, 64)
+    assert "lm_head.weight" not in sd                                            # tied to wte
+    assert all(v.dtype == torch.float16 for v in sd.values())
+    again = gpt2.random_state_dict(cfg, seed=0)
+    assert all(torch.equal(sd[k], again[k]) for k in sd)                         # seeded
+    # 2 layers x (qkv + proj + fc + proj2 + causal attention) + LM head, for 2 x 8 tokens
+    T, d, V = 16, 64, 50
+    per_layer = 2 * T * d * (3 * d + d + 4 * d + 4 * d) + 4 * 2 * 8 * 8 * d * 0.5
+    assert gpt2.GPT2Runner.flops_of(cfg, 2, 8) == 2 * per_layer + 2 * T * d * V
+    a = torch.zeros(1, 3, 50)
+    a[0, -1, [7, 3, 9, 1, 4]] = torch.tensor([5.0, 4.0, 3.0, 2.0, 1.0])
+    b = a.clone()
+    assert gpt2.top5_match(a, b) == (True, True)
+    b[0, -1, 7] = 5.1                                                            # within rtol 0.03
+    assert gpt2.top5_match(a, b) == (True, True)
+    b[0, -1, 3] = 6.0                                                            # order changes
+    assert gpt2.top5_match(a, b)[0] is False
+    with pytest.raises(KeyError):
+        gpt2.GPT2Runner(cfg, {k: v for k, v in sd.items() if "ln_f" not in k}, device="cpu")
