@@ -521,6 +521,8 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // set-up done; global memory is touched from here on
   const uint32_t tO = tmem_base + cfg::O_COL;
 
   if (warp == 0) {
@@ -1038,14 +1040,14 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   const int64_t ctas = (int64_t)p.ctas_per_bh * Z * H;
   if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
   if (wide)
-    attn_fwd_tc2_kernel<HD, false, 128><<<(unsigned)ctas, THREADS, Cfg2<HD, 128>::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2],
-                                                                                                  tm[3], p);
+    launch_pdl(attn_fwd_tc2_kernel<HD, false, 128>, dim3((unsigned)ctas), dim3(THREADS), (size_t)Cfg2<HD, 128>::SMEM_BYTES, st,
+               tm[0], tm[1], tm[2], tm[3], p);
   else if (two_buffers && x.mask)
-    attn_fwd_tc2_kernel<HD, true><<<(unsigned)ctas, THREADS, Cfg2<HD>::SMEM_BYTES_MASK, st>>>(tm[0], tm[1], tm[2],
-                                                                                             tm[3], p);
+    launch_pdl(attn_fwd_tc2_kernel<HD, true>, dim3((unsigned)ctas), dim3(THREADS), (size_t)Cfg2<HD>::SMEM_BYTES_MASK, st,
+               tm[0], tm[1], tm[2], tm[3], p);
   else if (two_buffers)
-    attn_fwd_tc2_kernel<HD, false><<<(unsigned)ctas, THREADS, Cfg2<HD>::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2], tm[3],
-                                                                                          p);
+    launch_pdl(attn_fwd_tc2_kernel<HD, false>, dim3((unsigned)ctas), dim3(THREADS), (size_t)Cfg2<HD>::SMEM_BYTES, st, tm[0],
+               tm[1], tm[2], tm[3], p);
   else
     attn_fwd_tc_kernel<HD><<<(unsigned)ctas, THREADS, cfg::SMEM_BYTES, st>>>(tm[0], tm[1], tm[2], p);
   return check_launch("attn_tc");

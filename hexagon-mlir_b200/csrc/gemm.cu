@@ -355,6 +355,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // barriers and TMEM are set up; global memory is touched from here on
 
   // Work items.  Items [0, full_items) are whole 128 x BN tiles; each remaining tile -- the ones of
   // the last, partial wave over the SMs -- is cut into `split` column slices of BN/split, so that
@@ -575,6 +577,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tc::cluster_sync_all();  // barriers of both CTAs are initialised before anything signals them
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();  // barriers and TMEM are set up; global memory is touched from here on
 
   constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
   const int num_tiles = tiles_m * tiles_n;       // tiles of 256 rows x OUT_COLS output columns
@@ -719,8 +723,9 @@ static int launch_tc_pair(const EpiArgs &epi, const StoreMap &sm, const CUtensor
   const int tiles_m = (M + 255) / 256, tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
   const int tiles = tiles_m * tiles_n;
   const int clusters = tiles < sm_count / 2 ? tiles : sm_count / 2;
-  kern<<<2 * clusters, launch_threads(M, N, K, EPI == 1 ? 1 : epi.act, sm_count), pair::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok,
-                                                        epi, sm.tm, sm.use, sm.r_vec);
+  launch_pdl(kern, dim3(2 * clusters), dim3(launch_threads(M, N, K, EPI == 1 ? 1 : epi.act, sm_count)),
+             (size_t)pair::SMEM_BYTES, st, tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok, epi, sm.tm, sm.use,
+             sm.r_vec);
   return check_launch("gemm_tc_pair");
 }
 
@@ -751,8 +756,9 @@ static int launch_tc(const EpiArgs &epi, const StoreMap &sm, const CUtensorMap &
   const int grid = items < sm_count ? items : sm_count;
   const uint32_t lbo = (uint32_t)option("gemm_b_lbo", BK * 128);
   const uint32_t sbo = (uint32_t)option("gemm_b_sbo", 1024);
-  kern<<<grid, launch_threads(M, N, K, EPI == 1 ? 1 : epi.act, sm_count), cfg::SMEM_BYTES, st>>>(tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n,
-                                               vec_ok, lbo, sbo, full_items, split, epi, sm.tm, sm.use, sm.r_vec);
+  launch_pdl(kern, dim3(grid), dim3(launch_threads(M, N, K, EPI == 1 ? 1 : epi.act, sm_count)), (size_t)cfg::SMEM_BYTES, st,
+             tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok, lbo, sbo, full_items, split, epi, sm.tm, sm.use,
+             sm.r_vec);
   return check_launch("gemm_tc");
 }
 

@@ -160,6 +160,8 @@ norm_ring_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict
   using Raw = decltype(Vec16<T>::raw);
   extern __shared__ uint8_t smem_raw[];
   ring::WarpRing rg = ring::setup(smem_raw, slots, slot_bytes, (dbg >> 8) & 1);
+  pdl_launch_dependents();
+  pdl_wait();  // the ring is set up; from here on global memory is touched
   const int store_mode = (dbg >> 4) & 3;
   dbg &= 15;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -347,9 +349,8 @@ static int launch_norm_ring(const T *x, T *y, const T *w, const T *b, float *mea
   }
   const int64_t groups = (rows + ring::WARPS - 1) / ring::WARPS;
   const int grid = (int)(groups < sm_count ? groups : sm_count);
-  kern<<<grid, ring::THREADS, lay.smem_bytes, st>>>(x, y, w, b, mean, rstd, rows, nvec, xs, ys, inv_n,
-                                                    eps, lay.slots, lay.slot_bytes, option("ring_map", 0),
-      option("ring_dbg", 0));
+  launch_pdl(kern, dim3(grid), dim3(ring::THREADS), (size_t)lay.smem_bytes, st, x, y, w, b, mean, rstd, rows, nvec, xs, ys,
+             inv_n, eps, lay.slots, lay.slot_bytes, (int)option("ring_map", 0), (int)option("ring_dbg", 0));
   return check_launch(RMS ? "rms_norm_ring" : "layer_norm_ring");
 }
 

@@ -23,6 +23,8 @@ softmax_rows_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, in
   __shared__ float red[3 * (THREADS / 32)];
   const int tr = threadIdx.x % TPR;
   const int rl = threadIdx.x / TPR;
+  pdl_launch_dependents();
+  pdl_wait();
 
   for (int64_t row0 = (int64_t)blockIdx.x * RPC; row0 < rows; row0 += (int64_t)gridDim.x * RPC) {
     const int64_t row = row0 + rl;
@@ -253,8 +255,8 @@ static int softmax_launch(const T *x, T *y, int64_t rows, int64_t cols, int64_t 
     constexpr int TH = CtaThreads<TPR>::value;                                                 \
     const int64_t ctas = (rows + TH / TPR - 1) / (TH / TPR);                                   \
     const int64_t cap = (int64_t)di.sm_count * 16;                                             \
-    softmax_rows_kernel<T, VPT, TPR, TH><<<(unsigned)(ctas < cap ? ctas : cap), TH, 0, st>>>(  \
-        x, y, rows, nvec, xs, ys);                                                             \
+    launch_pdl(softmax_rows_kernel<T, VPT, TPR, TH>, dim3((unsigned)(ctas < cap ? ctas : cap)), dim3(TH), 0, st, \
+               x, y, rows, nvec, xs, ys);                                                      \
   }
     HEXB_ROW_SHAPE_SWITCH(tpr, vpt, LAUNCH)
 #undef LAUNCH
