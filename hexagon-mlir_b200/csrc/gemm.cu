@@ -532,7 +532,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MAX_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
                     int64_t ldr, int tiles_m, int tiles_n, int vec_ok, const EpiArgs epi,
-                    const __grid_constant__ CUtensorMap tmC, int use_tma, int r_vec) {
+                    const __grid_constant__ CUtensorMap tmC, int use_tma, int r_vec, int full_items, int split) {
   using namespace pair;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
@@ -583,6 +583,24 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
   const int num_tiles = tiles_m * tiles_n;       // tiles of 256 rows x OUT_COLS output columns
   const int num_kb = (K + BK - 1) / BK;
+  // Work items: the tiles of the full waves, then the tiles of the last, partial wave cut into `split`
+  // column slices (256 x 128 with split == 2) so that the tail occupies the clusters for half a tile time.
+  const int num_items = full_items + (num_tiles - full_items) * split;
+  struct Item { int tm, col0, width; };
+  auto item_of = [&](int i) {
+    Item it;
+    int tile = i, sub = 0;
+    it.width = BN;
+    if (i >= full_items) {
+      const int k = i - full_items;
+      tile = full_items + k / split;
+      sub = k - (k / split) * split;
+      it.width = BN / split;
+    }
+    it.tm = tile % tiles_m;
+    it.col0 = (tile / tiles_m) * OUT_COLS + sub * it.width;
+    return it;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -590,24 +608,28 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int tm = tile % tiles_m, col0 = (tile / tiles_m) * OUT_COLS;
-        const int row0 = tm * 256 + (int)rank * BM;
-        // this CTA's half of the B tile: plain = columns [col0 + 128*rank, +128);
+      for (int item = cluster_id; item < num_items && ok; item += num_clusters) {
+        const Item w = item_of(item);
+        const int col0 = w.col0;
+        const int row0 = w.tm * 256 + (int)rank * BM;
+        const int half_w = w.width / 2;  // columns of B this CTA supplies: 128, or 64 for a slice
+        // this CTA's half of the B tile: plain = columns [col0 + half_w*rank, +half_w);
         // SwiGLU = rank 0 the gate columns [col0, +128), rank 1 the matching up columns [N + col0, +128)
-        const int bx = EPI == 1 ? (rank == 0 ? col0 : N + col0) : col0 + (int)rank * 128;
+        const int bx = EPI == 1 ? (rank == 0 ? col0 : N + col0) : col0 + (int)rank * half_w;
+        // bytes per CTA and stage: A, plus the B boxes actually loaded (the K-major form always loads its 128-row box)
+        const uint32_t stage_tx = (uint32_t)A_BYTES + (BT ? (uint32_t)B_HALF_BYTES : (uint32_t)half_w * BK * 2u);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!tc::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t sa = smem_addr + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
           const uint32_t leader_full = tc::map_to_rank(full_bar(stage), 0);
-          if (rank == 0) tc::mbar_arrive_expect_tx(full_bar(stage), 2u * STAGE_BYTES);  // both CTAs' bytes
+          if (rank == 0) tc::mbar_arrive_expect_tx(full_bar(stage), 2u * stage_tx);  // both CTAs' bytes
           tc::tma_load_2d_pair(sa, &tmA, kb * BK, row0, leader_full);
           if constexpr (BT) {
-            tc::tma_load_2d_pair(sb, &tmB, kb * BK, bx, leader_full);  // 128 rows of Bt x 64 k
+            tc::tma_load_2d_pair(sb, &tmB, kb * BK, bx, leader_full);  // 128 rows of Bt x 64 k (a slice uses the first 64)
           } else {
             tc::tma_load_2d_pair(sb, &tmB, bx, kb * BK, leader_full);
-            tc::tma_load_2d_pair(sb + BK * 128, &tmB, bx + 64, kb * BK, leader_full);
+            if (half_w > 64) tc::tma_load_2d_pair(sb + BK * 128, &tmB, bx + 64, kb * BK, leader_full);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -616,12 +638,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = tc::make_idesc_f16_f32(256, BN, 0, BT ? 0 : 1);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int t = 0;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++t) {
+      for (int item = cluster_id; item < num_items && ok; item += num_clusters, ++t) {
+        const uint32_t idesc = tc::make_idesc_f16_f32(256, item_of(item).width, 0, BT ? 0 : 1);
         const int acc = t & 1;
         if (!tc::mbar_wait(tempty_bar(acc), ((uint32_t)(t >> 1) & 1u) ^ 1u, abort_flag)) break;
         tc::tc_fence_after();
@@ -649,14 +671,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int halves = ((blockDim.x >> 5) - 2) >> 2, half = (warp - 2) >> 2;
     StoreStager<OutT> st = make_stager<OutT>(staging, staging_addr, &tmC, warp, lane);
     int t = 0;
-    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++t) {
-      const int tm = tile % tiles_m, col_base = (tile / tiles_m) * OUT_COLS;
+    for (int item = cluster_id; item < num_items; item += num_clusters, ++t) {
+      const Item w = item_of(item);
       const int acc = t & 1;
       if (!tc::mbar_wait(tfull_bar(acc), (uint32_t)(t >> 1) & 1u, abort_flag)) break;
       tc::tc_fence_after();
-      const int row0w = tm * 256 + (int)rank * BM + q * 32;
+      const int row0w = w.tm * 256 + (int)rank * BM + q * 32;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-      drain_accumulator<OutT, EPI, BN>(taddr, BN, col_base, row0w + lane, row0w, M, N, C, ldc, R, ldr, vec_ok, epi, halves,
+      drain_accumulator<OutT, EPI, BN>(taddr, w.width, w.col0, row0w + lane, row0w, M, N, C, ldc, R, ldr, vec_ok, epi, halves,
                                        half, st, use_tma, r_vec);
       tc::tc_fence_before();
       __syncwarp();
@@ -722,10 +744,21 @@ static int launch_tc_pair(const EpiArgs &epi, const StoreMap &sm, const CUtensor
   constexpr int OUT_COLS = EPI == 1 ? pair::BN / 2 : pair::BN;
   const int tiles_m = (M + 255) / 256, tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
   const int tiles = tiles_m * tiles_n;
-  const int clusters = tiles < sm_count / 2 ? tiles : sm_count / 2;
+  const int max_clusters = sm_count / 2;
+  // the tiles of the last partial wave are cut in two column slices when both halves still fit one wave
+  int full_items = tiles, split = 1;
+  if (EPI != 1 && tiles > max_clusters && option("gemm_tail_split", 1)) {
+    const int rem = tiles % max_clusters;
+    if (rem > 0 && 2 * rem <= max_clusters) {
+      full_items = tiles - rem;
+      split = 2;
+    }
+  }
+  const int items = full_items + (tiles - full_items) * split;
+  const int clusters = items < max_clusters ? items : max_clusters;
   launch_pdl(kern, dim3(2 * clusters), dim3(launch_threads(M, N, K, EPI == 1 ? 1 : epi.act, sm_count)),
              (size_t)pair::SMEM_BYTES, st, tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok, epi, sm.tm, sm.use,
-             sm.r_vec);
+             sm.r_vec, full_items, split);
   return check_launch("gemm_tc_pair");
 }
 
