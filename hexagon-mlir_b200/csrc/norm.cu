@@ -155,11 +155,13 @@ __global__ void __launch_bounds__(ring::THREADS, 1)
 norm_ring_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict__ w,
                  const T *__restrict__ b, float *__restrict__ mean_out, float *__restrict__ rstd_out,
                  int64_t rows, int nvec, int64_t xs, int64_t ys, float inv_n, float eps, int slots,
-                 int slot_bytes, int map, int dbg) {
+                 int slot_bytes, int map, int dbg, int out_slots) {
   constexpr int E = Vec16<T>::N;
   using Raw = decltype(Vec16<T>::raw);
   extern __shared__ uint8_t smem_raw[];
-  ring::WarpRing rg = ring::setup(smem_raw, slots, slot_bytes, (dbg >> 8) & 1);
+  // out_slots > 0: a finished row is written to a shared-memory slot and leaves as one bulk store
+  ring::WarpRing rg = ring::setup(smem_raw, slots, slot_bytes, (dbg >> 8) & 1, out_slots);
+  int n_out = 0;
   pdl_launch_dependents();
   pdl_wait();  // the ring is set up; from here on global memory is touched
   const int store_mode = (dbg >> 4) & 3;
@@ -285,6 +287,16 @@ norm_ring_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict
       if (++s == slots) { s = 0; phase ^= 1u; }
       continue;
     }
+    uint32_t oslot = 0;
+    if (out_slots) {
+      // the bulk store that last used this output slot has finished reading it
+      if (lane == 0) {
+        if (out_slots >= 2) tc::bulk_wait_group_read<1>();
+        else tc::bulk_wait_group_read<0>();
+      }
+      __syncwarp();
+      oslot = rg.out0 + (uint32_t)((n_out % out_slots) * slot_bytes);
+    }
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
       const int vi = lane + 32 * j;
@@ -304,7 +316,8 @@ norm_ring_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict
             for (int c = 0; c < 4; ++c)
               word(o, c) = h2_norm_affine(word(xr, c), mean, rstd, word(gr, c), word(br, c));
           }
-          ring::store_out16(yr + (int64_t)vi * E, o, store_mode, rg.policy);
+          if (out_slots) ring::sts128(oslot + (uint32_t)vi * 16u, o);
+          else ring::store_out16(yr + (int64_t)vi * E, o, store_mode, rg.policy);
         }
       } else if (vi < nvec) {
         float f[E], wf[E], bf[E];
@@ -323,11 +336,22 @@ norm_ring_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict
           f[e] = RMS ? (f[e] * rstd) * wf[e] : fmaf((f[e] - mean) * rstd, wf[e], bf[e]);
         Vec16<T> o;
         o.pack(f);
-        st_stream_as<Raw>(yr + (int64_t)vi * E, o.raw);
+        if (out_slots) ring::sts128(oslot + (uint32_t)vi * 16u, *reinterpret_cast<uint4 *>(&o.raw));
+        else st_stream_as<Raw>(yr + (int64_t)vi * E, o.raw);
       }
+    }
+    if (out_slots) {
+      tc::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        ring::bulk_store(yr, oslot, row_bytes);
+        tc::bulk_commit_group();
+      }
+      ++n_out;
     }
     if (++s == slots) { s = 0; phase ^= 1u; }
   }
+  if (out_slots && lane == 0) tc::bulk_wait_group_read<0>();  // shared memory outlives the last store's read
   if (*rg.abort_flag) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);  // let copies in flight land before the CTA retires
     if (threadIdx.x == 0) atomicExch(&g_norm_status, (int)HEXB_ERR_TIMEOUT);
@@ -338,7 +362,9 @@ template <typename T, int VPL, bool RMS>
 static int launch_norm_ring(const T *x, T *y, const T *w, const T *b, float *mean, float *rstd,
                             int64_t rows, int nvec, int64_t xs, int64_t ys, float inv_n, float eps,
                             int sm_count, cudaStream_t st) {
-  const ring::Layout lay = ring::make_layout(nvec * 16, 0);
+  // rows leave as one bulk store each from a per-warp output slot (measured 44.3 -> 43.7 us on [16384 x 4096] fp16)
+  const int out_slots = option("norm_bulk_store", 1) ? 1 : 0;
+  const ring::Layout lay = ring::make_layout(nvec * 16, 0, out_slots);
   auto kern = norm_ring_kernel<T, VPL, RMS>;
   static bool attr_done[64] = {};
   int dev = 0;
@@ -350,7 +376,7 @@ static int launch_norm_ring(const T *x, T *y, const T *w, const T *b, float *mea
   const int64_t groups = (rows + ring::WARPS - 1) / ring::WARPS;
   const int grid = (int)(groups < sm_count ? groups : sm_count);
   launch_pdl(kern, dim3(grid), dim3(ring::THREADS), (size_t)lay.smem_bytes, st, x, y, w, b, mean, rstd, rows, nvec, xs, ys,
-             inv_n, eps, lay.slots, lay.slot_bytes, (int)option("ring_map", 0), (int)option("ring_dbg", 0));
+             inv_n, eps, lay.slots, lay.slot_bytes, (int)option("ring_map", 0), (int)option("ring_dbg", 0), out_slots);
   return check_launch(RMS ? "rms_norm_ring" : "layer_norm_ring");
 }
 

@@ -29,6 +29,11 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
       : "memory");
 }
 
+// One row shared -> global as a single bulk store (bulk async-group completion).
+__device__ __forceinline__ void bulk_store(void *dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ uint64_t policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
@@ -72,14 +77,15 @@ struct Layout {
   int smem_bytes;     // dynamic shared memory of the CTA
 };
 
-inline Layout make_layout(int row_bytes, int extra_bytes = 0) {
+inline Layout make_layout(int row_bytes, int extra_bytes = 0, int out_slots = 0) {
   Layout l;
   l.slot_bytes = (row_bytes + 127) / 128 * 128;
   l.slots = option("ring_bytes_per_warp", RING_BYTES_PER_WARP) / l.slot_bytes;
   if (l.slots < 1) l.slots = 1;
   if (l.slots > MAX_SLOTS) l.slots = MAX_SLOTS;
   // [ring buffers][barriers][abort flag, pad to 128][extra][slack for the 128-byte alignment]
-  l.smem_bytes = WARPS * l.slots * l.slot_bytes + WARPS * MAX_SLOTS * 8 + 128 + extra_bytes + 128;
+  // [ring buffers][output slots][barriers][abort flag, pad to 128][extra][slack for the 128-byte alignment]
+  l.smem_bytes = WARPS * (l.slots + out_slots) * l.slot_bytes + WARPS * MAX_SLOTS * 8 + 128 + extra_bytes + 128;
   return l;
 }
 
@@ -91,6 +97,7 @@ struct WarpRing {
   int slots, slot_bytes;
   volatile int *abort_flag;
   uint32_t extra;      // shared address of the CTA-wide extra region (after barriers and flag)
+  uint32_t out0;       // shared address of this warp's first output slot (rows leave through bulk stores)
   uint64_t policy;     // L2 evict-first policy descriptor
   int load_hint;       // 1: bulk loads carry the evict-first hint
 
@@ -105,15 +112,18 @@ struct WarpRing {
 };
 
 // Carves the CTA's dynamic shared memory, initialises the barriers and returns this warp's ring.
-__device__ __forceinline__ WarpRing setup(uint8_t *smem_raw, int slots, int slot_bytes, int load_hint = 0) {
+__device__ __forceinline__ WarpRing setup(uint8_t *smem_raw, int slots, int slot_bytes, int load_hint = 0,
+                                          int out_slots = 0) {
   const uint32_t raw = tc::smem_u32(smem_raw);
   const uint32_t base = (raw + 127u) & ~127u;
   const int warp = threadIdx.x >> 5;
-  const uint32_t bars = base + (uint32_t)(WARPS * slots * slot_bytes);
+  const uint32_t outs = base + (uint32_t)(WARPS * slots * slot_bytes);
+  const uint32_t bars = outs + (uint32_t)(WARPS * out_slots * slot_bytes);
   WarpRing r;
   r.slots = slots;
   r.slot_bytes = slot_bytes;
   r.buf0 = base + (uint32_t)(warp * slots * slot_bytes);
+  r.out0 = outs + (uint32_t)(warp * out_slots * slot_bytes);
   r.bar0 = bars + (uint32_t)(warp * MAX_SLOTS * 8);
   r.abort_flag = reinterpret_cast<volatile int *>(smem_raw + (bars + WARPS * MAX_SLOTS * 8 - raw));
   r.extra = bars + WARPS * MAX_SLOTS * 8 + 128;
