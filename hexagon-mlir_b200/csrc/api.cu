@@ -44,7 +44,7 @@ int option(const char *key, int dflt) {
 }
 
 static const char *kKnownOptions[] = {
-    "softmax_vpt_max", "softmax_force_stream", "softmax_ring", "norm_ring", "norm_bulk_store", "ring_bytes_per_warp", "ring_map", "ring_dbg", "norm_vpt_max", "norm_force_stream",
+    "softmax_vpt_max", "softmax_force_stream", "softmax_ring", "softmax_bulk_store", "norm_ring", "norm_bulk_store", "ring_bytes_per_warp", "ring_map", "ring_dbg", "norm_vpt_max", "norm_force_stream",
     "norm_ctas_per_sm", "gemm_bn", "gemm_b_lbo", "gemm_b_sbo", "gemm_tail_split", "gemm_pair", "gemm_epi_warps", "gemm_tma_store", "gemm_force_simt", "attn_force_simt",
     "attn_v_lbo", "attn_v_sbo", "attn_tiles_per_cta", "attn_kernel", "attn_mask_tma", "scan_force_scalar", "scan_segments", "scan_kv", "decoder_fused_swiglu",
     "host_chunks", "pdl", nullptr};

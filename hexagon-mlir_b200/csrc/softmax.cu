@@ -80,11 +80,15 @@ static __device__ int g_softmax_status = 0;
 template <typename T, int VPL>
 __global__ void __launch_bounds__(ring::THREADS, 1)
 softmax_ring_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, int nvec, int64_t xs,
-                    int64_t ys, int slots, int slot_bytes, int map, int dbg) {
+                    int64_t ys, int slots, int slot_bytes, int map, int dbg, int out_slots) {
   constexpr int E = Vec16<T>::N;
   using Raw = decltype(Vec16<T>::raw);
   extern __shared__ uint8_t smem_raw[];
-  ring::WarpRing rg = ring::setup(smem_raw, slots, slot_bytes);
+  // out_slots > 0: a finished row is written to a shared-memory slot and leaves as one bulk store
+  ring::WarpRing rg = ring::setup(smem_raw, slots, slot_bytes, 0, out_slots);
+  int n_out = 0;
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t row_bytes = (uint32_t)nvec * 16u;
   const ring::RowWalk walk = ring::row_walk(rows, map);
@@ -138,6 +142,15 @@ softmax_ring_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, in
     sum = warp_sum(sum);
     const float inv = 1.0f / sum;
     T *yr = y + r * ys;
+    uint32_t oslot = 0;
+    if (out_slots) {
+      if (lane == 0) {  // the bulk store that last used this output slot has finished reading it
+        if (out_slots >= 2) tc::bulk_wait_group_read<1>();
+        else tc::bulk_wait_group_read<0>();
+      }
+      __syncwarp();
+      oslot = rg.out0 + (uint32_t)((n_out % out_slots) * slot_bytes);
+    }
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
       const int vi = lane + 32 * j;
@@ -146,11 +159,22 @@ softmax_ring_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, in
         for (int e = 0; e < E; ++e) f[j][e] *= inv;
         Vec16<T> o;
         o.pack(f[j]);
-        st_stream_as<Raw>(yr + (int64_t)vi * E, o.raw);
+        if (out_slots) ring::sts128(oslot + (uint32_t)vi * 16u, *reinterpret_cast<uint4 *>(&o.raw));
+        else st_stream_as<Raw>(yr + (int64_t)vi * E, o.raw);
       }
+    }
+    if (out_slots) {
+      tc::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        ring::bulk_store(yr, oslot, row_bytes);
+        tc::bulk_commit_group();
+      }
+      ++n_out;
     }
     if (++s == slots) { s = 0; phase ^= 1u; }
   }
+  if (out_slots && lane == 0) tc::bulk_wait_group_read<0>();
   if (*rg.abort_flag) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
     if (threadIdx.x == 0) atomicExch(&g_softmax_status, (int)HEXB_ERR_TIMEOUT);
@@ -160,7 +184,8 @@ softmax_ring_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, in
 template <typename T, int VPL>
 static int launch_softmax_ring(const T *x, T *y, int64_t rows, int nvec, int64_t xs, int64_t ys,
                                int sm_count, cudaStream_t st) {
-  const ring::Layout lay = ring::make_layout(nvec * 16);
+  const int out_slots = (int)option("softmax_bulk_store", 1);
+  const ring::Layout lay = ring::make_layout(nvec * 16, 0, out_slots);
   auto kern = softmax_ring_kernel<T, VPL>;
   static bool attr_done[64] = {};
   int dev = 0;
@@ -171,8 +196,8 @@ static int launch_softmax_ring(const T *x, T *y, int64_t rows, int nvec, int64_t
   }
   const int64_t groups = (rows + ring::WARPS - 1) / ring::WARPS;
   const int grid = (int)(groups < sm_count ? groups : sm_count);
-  kern<<<grid, ring::THREADS, lay.smem_bytes, st>>>(x, y, rows, nvec, xs, ys, lay.slots, lay.slot_bytes, option("ring_map", 0),
-      option("ring_dbg", 0));
+  launch_pdl(kern, dim3(grid), dim3(ring::THREADS), (size_t)lay.smem_bytes, st, x, y, rows, nvec, xs, ys, lay.slots,
+             lay.slot_bytes, (int)option("ring_map", 0), (int)option("ring_dbg", 0), out_slots);
   return check_launch("softmax_ring");
 }
 
