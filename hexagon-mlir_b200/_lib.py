@@ -68,6 +68,7 @@ PROTOTYPES = {
     "hexkl_matmul_f16f16_f32": (_i, [_i64, _i64, _i64, _vp, _vp, _vp]),
     "hexb_linear_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _vp]),
     "hexb_embedding_f16": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "hexb_iota": (_i, [_i, _vp, _i64, _vp]),
     "hexb_cumsum": (_i, [_i, _vp, _vp, _i64, _i64, _i64, _i, _vp]),
     "hexb_attention_fwd_ex": (_i, [C.POINTER(AttentionDesc), _vp]),
     "hexb_attention_fwd_f16": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, C.POINTER(_i64), _f, _i, _vp]),

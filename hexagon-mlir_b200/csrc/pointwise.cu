@@ -226,6 +226,14 @@ __global__ void __launch_bounds__(256) rope_rows_kernel(const T *__restrict__ x,
   }
 }
 
+// out[i] = i: what the reference's grid test computes when every program of a grid stores its
+// flattened id (test/python/triton/test_multidim_grid.py:21-37).
+template <typename T>
+__global__ void __launch_bounds__(256) iota_kernel(T *__restrict__ out, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256)
+    out[i] = from_f32<T>((float)i);
+}
+
 template <typename T, typename Op>
 static int launch_unary(const T *x, T *y, int64_t n, int sm, cudaStream_t st) {
   const int vec_ok = aligned16(x) && aligned16(y);
@@ -339,4 +347,19 @@ extern "C" int hexb_rope(int dtype, const void *x, void *out, int64_t B, int64_t
     rope_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>((const float *)x, (float *)out, B, L, H, D, x_strides[0],
         x_strides[1], x_strides[2], out_strides[0], out_strides[1], out_strides[2], k);
   return check_launch("rope");
+}
+
+extern "C" int hexb_iota(int dtype, void *out, int64_t n, void *stream) {
+  if (n < 0) return HEXB_ERR_BAD_ARG;
+  if (dtype != HEXB_DT_F16 && dtype != HEXB_DT_F32) return HEXB_ERR_UNSUPPORTED;
+  if (n == 0) return HEXB_OK;
+  if (!out) return HEXB_ERR_BAD_ARG;
+  DeviceInfo di;
+  if (int s = current_device(&di)) return s;
+  int64_t ctas = (n + 255) / 256;
+  const int64_t cap = (int64_t)di.sm_count * 16;
+  const unsigned grid = (unsigned)(ctas < cap ? ctas : cap);
+  if (dtype == HEXB_DT_F16) iota_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>((__half *)out, n);
+  else iota_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>((float *)out, n);
+  return check_launch("iota");
 }

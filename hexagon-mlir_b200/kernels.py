@@ -112,9 +112,40 @@ def _rsqrt_kernel(x_ptr, output_ptr, BLOCK_SIZE, _grid=(1,)):
     ops.unary("rsqrt", _flat(x_ptr, n), _flat(output_ptr, n))
 
 
-def _add_kernel(x_ptr, y_ptr, output_ptr, BLOCK_SIZE, _grid=(1,)):
-    n = _covered(x_ptr, BLOCK_SIZE, _grid)
+def _add_kernel(x_ptr, y_ptr, output_ptr, *rest, BLOCK_SIZE=None, n_elements=None, block_size=None, _grid=(1,)):
+    """Two reference kernels share this name: add_kernel(x, y, out, BLOCK_SIZE) (test_vec_add.py:19-25) and
+    add_kernel(x, y, out, n_elements, block_size) with a bounds mask (test_static_allocator_vadd.py:27-35)."""
+    rest = list(rest)
+    if BLOCK_SIZE is None and block_size is None and len(rest) == 1:
+        BLOCK_SIZE = rest.pop(0)                      # add_kernel(x, y, out, BLOCK_SIZE)
+    if rest:
+        n_elements = rest.pop(0)                      # add_kernel(x, y, out, n_elements, block_size[=...])
+    if rest:
+        block_size = rest.pop(0)
+    if rest:
+        raise TypeError("add_kernel: too many positional arguments")
+    bs = BLOCK_SIZE if BLOCK_SIZE is not None else block_size
+    if bs is None:
+        raise TypeError("add_kernel: BLOCK_SIZE (or block_size) is required")
+    n = _covered(x_ptr, bs, _grid)
+    if n_elements is not None:
+        n = min(n, int(n_elements))
     ops.binary("add", _flat(x_ptr, n), _flat(y_ptr, n), _flat(output_ptr, n))
+
+
+def _gelu_bptr_kernel(x_ptr, output_ptr, N, H, W, C):
+    """Whole-tensor GELU through block pointers over an [N, H, W, C] tensor (test_gelu_block_ptr.py:31-60)."""
+    n = int(N) * int(H) * int(W) * int(C)
+    ops.unary("gelu_tanh", _flat(x_ptr, n), _flat(output_ptr, n))
+
+
+def _flatten_pid(ptr, _grid=(1,)):
+    """Every program of a 1-, 2- or 3-D grid stores its flattened id at that index (test_multidim_grid.py:21-37):
+    the result is 0, 1, ..., prod(grid) - 1."""
+    progs = 1
+    for g in (_grid if isinstance(_grid, (tuple, list)) else (_grid,)):
+        progs *= int(g)
+    ops.iota(_flat(ptr, progs))
 
 
 def _add_kernel_scalar(x_ptr, y_ptr, output_ptr, n_elements, BLOCK_SIZE, _grid=(1,)):
@@ -188,6 +219,10 @@ _REGISTRY = {
     "attention_fwd_kernel": _attention_fwd_kernel,
     "silu_kernel": _silu_kernel,
     "gelu_kernel": _gelu_kernel,
+    "libd_gelu_kernel": _gelu_kernel,          # the same formula with libdevice.tanh (test_libd_gelu.py:35-49)
+    "gelu_bptr_kernel": _gelu_bptr_kernel,
+    "add_kernel_mulithreaded": _add_kernel,    # (sic) test_vec_add_multithread.py:23
+    "flatten_pid": _flatten_pid,
     "cos_kernel": _cos_kernel,
     "sin_kernel": _sin_kernel,
     "rsqrt_kernel": _rsqrt_kernel,

@@ -417,6 +417,19 @@ def binary(op: str, a, b, out) -> None:
         out.copy_(od)
 
 
+def iota(out) -> None:
+    """out[i] = i (reference: flatten_pid over a multi-dimensional grid, test_multidim_grid.py:21-37)."""
+    lib = _lib.load()
+    if not out.is_contiguous():
+        raise ValueError("iota: contiguous tensor expected")
+    host = out.device.type != "cuda"
+    od = torch.empty(out.shape, dtype=out.dtype, device="cuda") if host else out
+    with torch.cuda.device(od.device):
+        check(lib.hexb_iota(_dt(out), _ptr(od), out.numel(), _stream(od)), "iota")
+    if host:
+        out.copy_(od)
+
+
 def vec_sum(x, out) -> None:
     """out[0] = sum(x) with fp32 accumulation in a fixed order (reference: test_sum.py:31-36)."""
     lib = _lib.load()

@@ -187,6 +187,9 @@ enum { HEXB_OP_ADD = 1, HEXB_OP_SUB = 2, HEXB_OP_MUL = 3, HEXB_OP_DIV = 4 };
 int hexb_unary(int op, int dtype, const void *x, void *y, int64_t n, void *stream);
 int hexb_binary(int op, int dtype, const void *a, const void *b, void *y, int64_t n, void *stream);
 int hexb_sum(int dtype, const void *x, void *out, int64_t n, void *stream);
+/* out[i] = i for i < n.  Replaces: flatten_pid(ptr) launched on a 1-, 2- or 3-D grid, where every
+ * program stores its flattened id at that index (test/python/triton/test_multidim_grid.py:21-37). */
+int hexb_iota(int dtype, void *out, int64_t n, void *stream);
 int hexb_rope(int dtype, const void *x, void *out, int64_t B, int64_t L, int64_t H, int64_t D,
               const int64_t *x_strides, const int64_t *out_strides, float theta, void *stream);
 

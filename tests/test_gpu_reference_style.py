@@ -188,3 +188,83 @@ def test_silu(num_elements, num_threads, dtype):
     silu_kernel[(num_threads,)](x, output, BLOCK_SIZE=triton.next_power_of_2(num_elements // num_threads),
                                 enableMultiThreading=num_threads == 1)
     assert torch.allclose(output, F.silu(x), atol=1e-2)
+
+
+# ------------------------------------------------------------------ the remaining Triton-test kernels
+def test_gelu_block_ptr():
+    """test_gelu_block_ptr.py: one program, block pointers over an [N, H, W, C] fp16 tensor."""
+    N, H, W, C = 16, 16, 128, 2
+
+    @triton.jit
+    def gelu_bptr_kernel(x_ptr, output_ptr, N, H, W, C):
+        ...
+
+    x = torch.rand(N, H, W, C, dtype=torch.float16)
+    output = torch.empty_like(x, dtype=torch.float16)
+    gelu_bptr_kernel[(1,)](x, output, N, H, W, C)
+    assert torch.allclose(output, F.gelu(x.float(), approximate="tanh").half(), atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_libd_gelu(dtype):
+    """test_libd_gelu.py: the GELU formula with libdevice.tanh, 4 programs."""
+    NUM_ELEMENTS, NUM_THREADS = 16384, 4
+
+    @triton.jit
+    @parameterize_func_name(dtype)
+    def libd_gelu_kernel(x_ptr, output_ptr, BLOCK_SIZE):
+        ...
+
+    x = torch.rand(NUM_ELEMENTS, dtype=dtype)
+    output = torch.empty_like(x, dtype=dtype)
+    libd_gelu_kernel[(NUM_THREADS,)](x, output, BLOCK_SIZE=NUM_ELEMENTS // NUM_THREADS, enableVTCMTiling=False,
+                                     enableConvertToHexagonmem=False)
+    assert torch.allclose(output, F.gelu(x, approximate="tanh"), atol=1e-2 if dtype == torch.float16 else 1e-5)
+
+
+def test_vec_add_multithread():
+    NUM_ELEMENTS, NUM_THREADS = 16384, 4
+
+    @triton.jit
+    def add_kernel_mulithreaded(x_ptr, y_ptr, output_ptr, BLOCK_SIZE):
+        ...
+
+    x, y = torch.rand(NUM_ELEMENTS), torch.rand(NUM_ELEMENTS)
+    output = torch.empty_like(x)
+    add_kernel_mulithreaded[(NUM_THREADS,)](x, y, output, BLOCK_SIZE=NUM_ELEMENTS // NUM_THREADS,
+                                            enableMultiThreading=False, enableVTCMTiling=False,
+                                            enableConvertToHexagonmem=False, enableHexagonmemCopyToDMA=False)
+    assert torch.allclose(output, x + y)
+
+
+@pytest.mark.parametrize("use_scratch", [False, True], ids=["no-scratch", "vtcm-scratch"])
+@pytest.mark.parametrize("grid", [(1,), (2,), (4,)], ids=["grid1", "grid2", "grid4"])
+def test_static_allocator_vadd(grid, use_scratch):
+    """test_static_allocator_vadd.py: add_kernel(x, y, out, n_elements, block_size=...) with a scratch option."""
+
+    @triton.jit
+    def add_kernel(x_ptr, y_ptr, output_ptr, n_elements, block_size):
+        ...
+
+    N = 131072
+    x, y = torch.rand(N), torch.rand(N)
+    output = torch.empty_like(x)
+    alignment = 2048
+    per_instance_vtcm = (1 * 1024 * 1024) & ~(alignment - 1)
+    scratch = per_instance_vtcm if use_scratch else 0
+    add_kernel[grid](x, y, output, N, block_size=N // grid[0], enableHexagonmemCopyToDMA=False, scratch=scratch)
+    assert torch.allclose(output, x + y)
+
+
+def test_multidim_grid():
+    """test_multidim_grid.py: every program of a (10, 5, 2) grid stores its flattened id."""
+    GRID = (10, 5, 2)
+
+    @triton.jit
+    def flatten_pid(ptr):
+        ...
+
+    num_elements = 100
+    result = torch.zeros(num_elements)
+    flatten_pid[GRID](result, enableVTCMTiling=True, enableConvertToHexagonmem=True, enableHexagonmemCopyToDMA=True)
+    assert torch.allclose(result, torch.arange(num_elements, dtype=torch.float))
