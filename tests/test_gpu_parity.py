@@ -669,3 +669,43 @@ def test_attention_selectable_kernels_agree_with_default(dev, which, causal):
             hexb200.set_option("attn_kernel", 2)
         assert hexb200.device_status() == 0
         assert O.max_rel_err(b.cpu(), a.cpu()) < 2e-3
+
+
+def test_entry_points_are_thread_safe_and_stream_ordered(dev):
+    """Two host threads drive the library on their own streams at the same time (ctypes releases the GIL
+    for the duration of a call); every result must equal the single-threaded one."""
+    import threading
+
+    g = torch.Generator().manual_seed(21)
+    a = torch.randn(512, 256, generator=g).half().to(dev)
+    b = torch.randn(256, 384, generator=g).half().to(dev)
+    x = torch.randn(1024, 1024, generator=g).to(dev)
+    ref_c = torch.empty(512, 384, dtype=torch.float16, device=dev)
+    ref_y = torch.empty_like(x)
+    ops.matmul(a, b, ref_c)
+    ops.softmax(x, ref_y)
+    torch.cuda.synchronize()
+    errors = []
+
+    def worker(seed):
+        try:
+            s = torch.cuda.Stream(device=dev)
+            with torch.cuda.stream(s):
+                c = torch.empty_like(ref_c)
+                y = torch.empty_like(ref_y)
+                for _ in range(40):
+                    ops.matmul(a, b, c)
+                    ops.softmax(x, y)
+                s.synchronize()
+                if not (torch.equal(c, ref_c) and torch.equal(y, ref_y)):
+                    errors.append(f"thread {seed}: result differs")
+        except Exception as e:  # noqa: BLE001
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(3)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert hexb200.device_status() == 0
