@@ -5,8 +5,9 @@
 
 A step is one pass of the hot path over one batch of seeded synthetic input.  The headline workload
 is LayerNorm fp16 [16384 x 4096] (the benchmark's second configuration, the bandwidth-bound one the
-HBM GB/s metric is quoted on); `--workload` selects softmax / gemm / attention / decoder instead, and
-the default single-GPU run also measures those four and lists them under "workloads".  Rank 0 prints
+HBM GB/s metric is quoted on); `--workload` selects softmax / gemm / attention / decoder (the benchmark's
+other configurations) or gpt2 (the reference's two-layer GPT-2 test) instead, and the default single-GPU
+run also measures those five and lists them under "workloads".  Rank 0 prints
 ONE JSON line.  With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs the
 full-size workload on its own GPU (weak scaling: independent row blocks / (batch, head) pairs /
 sequences, no data-path collective); the optional all-gather of output shards is timed apart.
@@ -519,7 +520,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="layernorm", choices=sorted(WORKLOADS))
-    ap.add_argument("--no-extras", action="store_true", help="skip the other four configurations and the CPU baseline")
+    ap.add_argument("--no-extras", action="store_true", help="skip the other workloads and the CPU baseline")
     ap.add_argument("--eager", action="store_true", help="time K eager launches instead of one CUDA-graph replay of them")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement (profiling runs)")
     ap.add_argument("--gather", action="store_true", help="also time the all-gather of output shards (N > 1)")
