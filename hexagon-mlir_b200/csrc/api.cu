@@ -76,6 +76,36 @@ int current_device(DeviceInfo *out) {
   return HEXB_OK;
 }
 
+// ---- library-owned memory pool for stream-ordered scratch
+int scratch_alloc(void **ptr, size_t bytes, cudaStream_t st) {
+  static cudaMemPool_t pools[64] = {};
+  int dev = 0;
+  HEXB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return HEXB_ERR_NO_DEVICE;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!pools[dev]) {
+      cudaMemPoolProps props = {};
+      props.allocType = cudaMemAllocationTypePinned;
+      props.handleTypes = cudaMemHandleTypeNone;
+      props.location.type = cudaMemLocationTypeDevice;
+      props.location.id = dev;
+      cudaMemPool_t pool = nullptr;
+      HEXB_CUDA_OK(cudaMemPoolCreate(&pool, &props));
+      unsigned long long keep = ~0ull;  // freed blocks stay in the pool
+      HEXB_CUDA_OK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+      pools[dev] = pool;
+    }
+  }
+  HEXB_CUDA_OK(cudaMallocFromPoolAsync(ptr, bytes, pools[dev], st));
+  return HEXB_OK;
+}
+
+int scratch_free(void *ptr, cudaStream_t st) {
+  if (ptr) HEXB_CUDA_OK(cudaFreeAsync(ptr, st));
+  return HEXB_OK;
+}
+
 // ---- per-device staging memory for the `_host` entry points (grow-only, released on request).
 struct Staging {
   void *ptr = nullptr;

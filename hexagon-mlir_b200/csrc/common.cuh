@@ -28,6 +28,13 @@ struct DeviceInfo {
 // Properties of the current device (cached per device id); status != HEXB_OK if there is none.
 int current_device(DeviceInfo *out);
 
+// Stream-ordered scratch for the few kernels that need a small workspace (segment totals of a scan,
+// partial sums): allocated from a memory pool the library owns per device, whose release threshold
+// keeps freed blocks cached, so a call costs no device allocation after the first and the
+// application's own pools are not touched.
+int scratch_alloc(void **ptr, size_t bytes, cudaStream_t st);
+int scratch_free(void *ptr, cudaStream_t st);
+
 #define HEXB_CUDA_OK(expr)                                   \
   do {                                                       \
     cudaError_t _e = (expr);                                 \

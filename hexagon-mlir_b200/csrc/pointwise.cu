@@ -156,11 +156,11 @@ static int launch_sum(const T *x, T *out, int64_t n, int sm, cudaStream_t st) {
   const int64_t cap = (int64_t)sm * 8;
   const int grid = (int)(ctas < cap ? ctas : cap);
   float *partial = nullptr;
-  HEXB_CUDA_OK(cudaMallocAsync(reinterpret_cast<void **>(&partial), (size_t)grid * sizeof(float), st));
+  if (int e = scratch_alloc(reinterpret_cast<void **>(&partial), (size_t)grid * sizeof(float), st)) return e;
   sum_partial_kernel<T><<<grid, 256, 0, st>>>(x, partial, n, aligned16(x) ? 1 : 0);
   sum_final_kernel<T><<<1, 1024, 0, st>>>(partial, out, grid);
   const int rc = check_launch("sum");
-  HEXB_CUDA_OK(cudaFreeAsync(partial, st));
+  if (int e = scratch_free(partial, st)) return e;
   return rc;
 }
 

@@ -152,37 +152,70 @@ __global__ void __launch_bounds__(32) segment_offsets_kernel(const A *__restrict
 // inner > 1: one thread per (outer, inner) column and segment of the axis (blockIdx.y), coalesced over
 // inner; eight loads are issued before the dependent additions.  MODE as above; totals and offsets are
 // laid out [segment][column].
-template <typename T, int MODE>
+// VEC: adjacent columns one thread carries (1, or a 16-byte vector of them when inner allows it).
+template <typename T, int MODE, int VEC>
 __global__ void __launch_bounds__(THREADS)
 cumsum_strided_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t outer, int64_t len, int64_t inner,
                       int reverse, int64_t seg_len, const typename AccOf<T>::type *__restrict__ offsets,
                       typename AccOf<T>::type *__restrict__ totals) {
   using A = typename AccOf<T>::type;
-  constexpr int U = 8;
+  constexpr int U = VEC == 1 ? 8 : (sizeof(T) == 2 ? 4 : 8);
   const int64_t cols = outer * inner;
-  const int64_t col = (int64_t)blockIdx.x * THREADS + threadIdx.x;
-  if (col >= cols) return;
-  const int64_t o = col / inner, i = col - o * inner;
+  const int64_t groups_per_row = inner / VEC;
+  const int64_t grp = (int64_t)blockIdx.x * THREADS + threadIdx.x;
+  if (grp >= outer * groups_per_row) return;
+  const int64_t o = grp / groups_per_row, i = (grp - o * groups_per_row) * VEC;
+  const int64_t col = o * inner + i;
   const T *xp = x + o * len * inner + i;
   T *yp = y + o * len * inner + i;
   const int64_t p0 = (int64_t)blockIdx.y * seg_len;
   const int64_t p1 = p0 + seg_len < len ? p0 + seg_len : len;
-  A acc = (MODE == 0 && offsets) ? offsets[(int64_t)blockIdx.y * cols + col] : A(0);
+  A acc[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) acc[e] = (MODE == 0 && offsets) ? offsets[(int64_t)blockIdx.y * cols + col + e] : A(0);
   for (int64_t q0 = p0; q0 < p1; q0 += U) {
-    A v[U];
+    A v[U][VEC];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t p = q0 + u;
-      v[u] = p < p1 ? load_acc<T, A>(xp[(reverse ? len - 1 - p : p) * inner]) : A(0);
+      const int64_t l = reverse ? len - 1 - p : p;
+      if constexpr (VEC == 1) {
+        v[u][0] = p < p1 ? load_acc<T, A>(xp[l * inner]) : A(0);
+      } else {
+        if (p < p1) {
+          const uint4 raw = ld_stream16(xp + l * inner);
+          const T *t = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) v[u][e] = load_acc<T, A>(t[e]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) v[u][e] = A(0);
+        }
+      }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t p = q0 + u;
-      acc += v[u];
-      if (MODE == 0 && p < p1) yp[(reverse ? len - 1 - p : p) * inner] = store_acc<T, A>(acc);
+      const int64_t l = reverse ? len - 1 - p : p;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] += v[u][e];
+      if (MODE == 0 && p < p1) {
+        if constexpr (VEC == 1) {
+          yp[l * inner] = store_acc<T, A>(acc[0]);
+        } else {
+          uint4 raw;
+          T *t = reinterpret_cast<T *>(&raw);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) t[e] = store_acc<T, A>(acc[e]);
+          st_stream16(yp + l * inner, raw);
+        }
+      }
     }
   }
-  if (MODE == 1) totals[(int64_t)blockIdx.y * cols + col] = acc;
+  if (MODE == 1) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) totals[(int64_t)blockIdx.y * cols + col + e] = acc[e];
+  }
 }
 
 template <typename A>
@@ -221,7 +254,7 @@ static int launch_rows(const T *x, T *y, int64_t outer, int64_t len, int reverse
   A *scratch = nullptr;
   if (segs > 1) {
     // stream-ordered scratch for the segment totals and offsets (a few KiB)
-    HEXB_CUDA_OK(cudaMallocAsync(reinterpret_cast<void **>(&scratch), (size_t)ctas * 2 * sizeof(A), st));
+    if (int e = scratch_alloc(reinterpret_cast<void **>(&scratch), (size_t)ctas * 2 * sizeof(A), st)) return e;
     cumsum_rows_kernel<T, 1, VEC, KV><<<(unsigned)ctas, THREADS, 0, st>>>(x, y, len, seg_len, (int)segs, reverse,
                                                                           nullptr, scratch);
     segment_offsets_kernel<A><<<(unsigned)outer, 32, 0, st>>>(scratch, scratch + ctas, (int)segs);
@@ -229,7 +262,7 @@ static int launch_rows(const T *x, T *y, int64_t outer, int64_t len, int reverse
   cumsum_rows_kernel<T, 0, VEC, KV><<<(unsigned)ctas, THREADS, 0, st>>>(x, y, len, seg_len, (int)segs, reverse,
                                                                         segs > 1 ? scratch + ctas : nullptr, nullptr);
   const int rc = check_launch("cumsum_rows");
-  if (scratch) HEXB_CUDA_OK(cudaFreeAsync(scratch, st));
+  if (int e = scratch_free(scratch, st)) return e;
   return rc;
 }
 
@@ -240,27 +273,37 @@ static int run(const T *x, T *y, int64_t outer, int64_t len, int64_t inner, int 
   if (int e = current_device(&di)) return e;
   if (inner > 1) {
     const int64_t cols = outer * inner;
+    constexpr int EV = 16 / (int)sizeof(T);
+    const bool vecs = inner % EV == 0 && aligned16(x) && aligned16(y) && !option("scan_force_scalar", 0);
+    const int64_t groups = vecs ? cols / EV : cols;            // threads along the columns
+    const int64_t grp_ctas = (groups + THREADS - 1) / THREADS;
     const int64_t col_ctas = (cols + THREADS - 1) / THREADS;
     if (col_ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
     // enough threads to keep the memory system busy: about 2048 per SM, segments of at least 64 steps
-    int64_t segs = (2048ll * di.sm_count + cols - 1) / cols;
+    int64_t segs = (2048ll * di.sm_count + groups - 1) / groups;
     if (segs > (len + 63) / 64) segs = (len + 63) / 64;
-    if (segs > 65535) segs = 65535;
+    // the offsets pass walks the segments serially per column and the scratch is [segments][columns]:
+    // keep both small (at most 64 segments, at most 16 MiB of totals + offsets)
+    if (segs > 64) segs = 64;
+    const int64_t by_scratch = ((int64_t)16 << 20) / (cols * 2 * (int64_t)sizeof(A));
+    if (segs > by_scratch) segs = by_scratch;
     if (segs < 1) segs = 1;
     if (int64_t forced = option("scan_segments", 0)) segs = forced < 65535 ? forced : 65535;
     const int64_t seg_len = (len + segs - 1) / segs;
     segs = (len + seg_len - 1) / seg_len;
-    const dim3 grid((unsigned)col_ctas, (unsigned)segs);
+    const dim3 grid((unsigned)grp_ctas, (unsigned)segs);
     A *scratch = nullptr;
     if (segs > 1) {
-      HEXB_CUDA_OK(cudaMallocAsync(reinterpret_cast<void **>(&scratch), (size_t)(cols * segs) * 2 * sizeof(A), st));
-      cumsum_strided_kernel<T, 1><<<grid, THREADS, 0, st>>>(x, y, outer, len, inner, reverse, seg_len, nullptr, scratch);
+      if (int e = scratch_alloc(reinterpret_cast<void **>(&scratch), (size_t)(cols * segs) * 2 * sizeof(A), st)) return e;
+      if (vecs) cumsum_strided_kernel<T, 1, EV><<<grid, THREADS, 0, st>>>(x, y, outer, len, inner, reverse, seg_len, nullptr, scratch);
+      else cumsum_strided_kernel<T, 1, 1><<<grid, THREADS, 0, st>>>(x, y, outer, len, inner, reverse, seg_len, nullptr, scratch);
       strided_offsets_kernel<A><<<(unsigned)col_ctas, THREADS, 0, st>>>(scratch, scratch + cols * segs, cols, (int)segs);
     }
-    cumsum_strided_kernel<T, 0><<<grid, THREADS, 0, st>>>(x, y, outer, len, inner, reverse, seg_len,
-                                                          segs > 1 ? scratch + cols * segs : nullptr, nullptr);
+    const A *offs = segs > 1 ? scratch + cols * segs : nullptr;
+    if (vecs) cumsum_strided_kernel<T, 0, EV><<<grid, THREADS, 0, st>>>(x, y, outer, len, inner, reverse, seg_len, offs, nullptr);
+    else cumsum_strided_kernel<T, 0, 1><<<grid, THREADS, 0, st>>>(x, y, outer, len, inner, reverse, seg_len, offs, nullptr);
     const int rc = check_launch("cumsum_strided");
-    if (scratch) HEXB_CUDA_OK(cudaFreeAsync(scratch, st));
+    if (int e = scratch_free(scratch, st)) return e;
     return rc;
   }
   constexpr int E = 16 / (int)sizeof(T);
