@@ -103,9 +103,14 @@ class GPT2Runner:
             }
         return self._bufs[key]
 
-    def forward(self, input_ids: torch.Tensor, logits_dtype=torch.float32, graph: bool = False) -> torch.Tensor:
+    def forward(self, input_ids: torch.Tensor, logits_dtype=torch.float32, graph: bool = False,
+                last_only: bool = False) -> torch.Tensor:
         """input_ids: int64 [batch, seq] on the runner's device.  Returns logits [batch, seq, vocab]
         (a buffer owned by the runner, overwritten by the next call with the same shape).
+
+        last_only=True computes the final LayerNorm and the LM head for the last position of every
+        sequence only and returns [batch, 1, vocab]: what next-token prediction -- and the reference's
+        top-5 comparison -- reads; the LM head is more than half of a full forward pass.
 
         graph=True replays the 17 launches as one CUDA graph captured on the first call with this
         (batch, seq, logits dtype): for short prompts the launches, not the kernels, set the latency."""
@@ -116,22 +121,22 @@ class GPT2Runner:
         if S > cfg.n_positions:
             raise ValueError("GPT2Runner: sequence longer than n_positions")
         if not graph:
-            return self._forward(input_ids.contiguous(), logits_dtype)
-        key = (B, S, logits_dtype)
+            return self._forward(input_ids.contiguous(), logits_dtype, last_only)
+        key = (B, S, logits_dtype, last_only)
         if key not in self._graphs:
             static_ids = input_ids.clone()
-            self._forward(static_ids, logits_dtype)          # first call outside capture: one-time set-up
+            self._forward(static_ids, logits_dtype, last_only)   # first call outside capture: one-time set-up
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                out = self._forward(static_ids, logits_dtype)
+                out = self._forward(static_ids, logits_dtype, last_only)
             self._graphs[key] = (g, static_ids, out)
         g, static_ids, out = self._graphs[key]
         static_ids.copy_(input_ids)
         g.replay()
         return out
 
-    def _forward(self, input_ids: torch.Tensor, logits_dtype) -> torch.Tensor:
+    def _forward(self, input_ids: torch.Tensor, logits_dtype, last_only: bool = False) -> torch.Tensor:
         cfg, w = self.cfg, self.w
         B, S = input_ids.shape
         d, H, D = cfg.n_embd, cfg.n_head, self.head_dim
@@ -150,6 +155,13 @@ class GPT2Runner:
             ops.layer_norm(x2, b["ln"], w[p + "ln_2.weight"], w[p + "ln_2.bias"], eps=cfg.layer_norm_epsilon)
             ops.linear(b["ln"], w[p + "mlp.c_fc.weight"], b["fc"], bias=w[p + "mlp.c_fc.bias"], act="gelu_tanh")
             ops.linear(b["fc"], w[p + "mlp.c_proj.weight"], x, bias=w[p + "mlp.c_proj.bias"], residual=x2)
+        if last_only:
+            last = x[S - 1::S]                               # the last position of every sequence: [B, d], row stride S * d
+            ln = b["ln"][:B]
+            ops.layer_norm(last, ln, w["transformer.ln_f.weight"], w["transformer.ln_f.bias"], eps=cfg.layer_norm_epsilon)
+            logits = b["logits"][:B, :cfg.vocab_size]
+            ops.matmul_nt(ln, w["transformer.wte.weight"], logits)
+            return logits.unflatten(0, (B, 1))
         ops.layer_norm(x, b["ln"], w["transformer.ln_f.weight"], w["transformer.ln_f.bias"], eps=cfg.layer_norm_epsilon)
         logits = b["logits"][:, :cfg.vocab_size]
         ops.matmul_nt(b["ln"], w["transformer.wte.weight"], logits)

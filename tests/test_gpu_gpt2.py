@@ -142,3 +142,16 @@ def test_linear_residual_in_place(M, N, K):
     ref = x.float() + a.float() @ w.float() + bias.float()
     assert O.max_rel_err(xd.cpu(), ref) < REL_F16
     assert hexb200.device_status() == 0
+
+
+def test_gpt2_last_position_only():
+    cfg = gpt2.GPT2Config()
+    runner = gpt2.GPT2Runner(cfg, gpt2.random_state_dict(cfg, seed=6), device=dev)
+    ids = torch.randint(0, cfg.vocab_size, (3, 200), generator=torch.Generator().manual_seed(2)).to(dev)
+    full = runner.forward(ids)[:, -1:, :].clone()
+    last = runner.forward(ids, last_only=True)
+    assert last.shape == (3, 1, cfg.vocab_size)
+    assert O.max_rel_err(last.cpu(), full.cpu()) < 1e-3
+    again = runner.forward(ids, last_only=True, graph=True)
+    assert torch.equal(again, last)
+    assert hexb200.device_status() == 0
