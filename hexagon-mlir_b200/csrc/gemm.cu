@@ -128,6 +128,17 @@ __device__ __forceinline__ float gelu_tanh_f32(float x) {
   return 0.5f * x * (2.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u)));
 }
 
+// For fp16 outputs: tanh as one special-function instruction (absolute error ~5e-4, the size of the
+// output's own rounding step); fp32 outputs keep the exp-based form above.
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  const float u = 0.797885f * x + 0.035677f * x * x * x;
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  const float hx = 0.5f * x;
+  return fmaf(hx, t, hx);
+}
+
+template <bool FAST>
 __device__ __forceinline__ void apply_bias_act(uint32_t (&acc)[32], const EpiArgs &epi, int col0, int N) {
   if (epi.bias) {
     if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(epi.bias + col0) & 15u) == 0) {
@@ -148,7 +159,8 @@ __device__ __forceinline__ void apply_bias_act(uint32_t (&acc)[32], const EpiArg
   }
   if (epi.act == 1) {
 #pragma unroll
-    for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(gelu_tanh_f32(__uint_as_float(acc[e])));
+    for (int e = 0; e < 32; ++e)
+      acc[e] = __float_as_uint(FAST ? gelu_tanh_fast(__uint_as_float(acc[e])) : gelu_tanh_f32(__uint_as_float(acc[e])));
   }
 }
 
@@ -294,7 +306,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int width, int
       tc::tmem_ld_wait();
     }
     const int col0 = col_base + c * 32;
-    if constexpr (EPI == 2) apply_bias_act(v, epi, col0, N);
+    if constexpr (EPI == 2) apply_bias_act<sizeof(OutT) == 2>(v, epi, col0, N);
     if (use_tma) st.put32(v, rrow, r_vec, col0, row0w, N);
     else if (row < M && col0 < N) store_row_chunk<OutT>(crow, rrow, v, col0, N, vec_ok != 0);
   }
