@@ -140,3 +140,42 @@ def test_cumsum_random_shapes(seed):
     ops.cumsum(xf.to(dev), outf, axis=axis, reverse=reverse)
     reff = xf.double().flip(axis).cumsum(axis).flip(axis) if reverse else xf.double().cumsum(axis)
     assert (outf.cpu().double() - reff).abs().max() <= 1e-3 * max(1.0, reff.abs().max().item()), (shape, axis, reverse)
+
+
+def test_empty_and_degenerate_inputs_of_the_newer_entry_points():
+    """Zero-sized problems return without launching; impossible ones are refused with a status, not a fault."""
+    lib = hexb200.load()
+    h = torch.float16
+    # linear: M == 0 / N == 0 are no-ops, K == 0 gives bias (+ residual)
+    a0 = torch.empty(0, 16, dtype=h, device=dev)
+    w = torch.randn(16, 8, device=dev).half()
+    ops.linear(a0, w, torch.empty(0, 8, dtype=h, device=dev))
+    ak = torch.empty(4, 0, dtype=h, device=dev)
+    wk = torch.empty(0, 8, dtype=h, device=dev)
+    bias = torch.randn(8, device=dev).half()
+    c = torch.full((4, 8), float("nan"), dtype=h, device=dev)
+    ops.linear(ak, wk, c, bias=bias)
+    assert torch.equal(c, bias.expand(4, 8))
+    # cumsum: any zero extent is a no-op; a length-1 axis copies
+    for shape in [(0, 5), (5, 0), (3, 0, 2)]:
+        x = torch.empty(shape, device=dev)
+        ops.cumsum(x, torch.empty_like(x), axis=1)
+    x1 = torch.randn(7, 1, 3, device=dev)
+    y1 = torch.empty_like(x1)
+    ops.cumsum(x1, y1, axis=1)
+    assert torch.equal(x1, y1)
+    # embedding: no tokens
+    wte, wpe = torch.randn(10, 8, device=dev).half(), torch.randn(4, 8, device=dev).half()
+    ops.embedding(wte, wpe, torch.empty(0, 3, dtype=torch.int64, device=dev), torch.empty(0, 3, 8, dtype=h, device=dev))
+    # attention: no keys cannot be normalised -> refused; no queries is a no-op
+    q = torch.randn(1, 1, 4, 64, device=dev).half()
+    k0 = torch.empty(1, 1, 0, 64, dtype=h, device=dev)
+    with pytest.raises(hexb200.HexbError):
+        ops.attention_ex(q, k0, k0, torch.empty_like(q))
+    q0 = torch.empty(1, 1, 0, 64, dtype=h, device=dev)
+    kk = torch.randn(1, 1, 5, 64, device=dev).half()
+    ops.attention_ex(q0, kk, kk, torch.empty_like(q0))
+    # iota: nothing to fill
+    ops.iota(torch.empty(0, device=dev))
+    assert hexb200.device_status() == 0
+    assert lib.hexb_cumsum(99, None, None, 1, 1, 1, 0, None) != 0          # unknown dtype
