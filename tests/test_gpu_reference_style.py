@@ -268,3 +268,33 @@ def test_multidim_grid():
     result = torch.zeros(num_elements)
     flatten_pid[GRID](result, enableVTCMTiling=True, enableConvertToHexagonmem=True, enableHexagonmemCopyToDMA=True)
     assert torch.allclose(result, torch.arange(num_elements, dtype=torch.float))
+
+
+# ------------------------------------------------------------------ the single-operator torch-mlir tests
+# test/python/torch-mlir/test_{gelu,softmax,layernorm}_torch.py compile a one-node torch module and compare
+# with eager PyTorch on a 128 x 128 fp16 input; here the node is the library call, the comparison is theirs.
+def test_gelu_torch_case():
+    from hexb200 import ops
+    inp = torch.rand(128, 128, dtype=torch.float16)
+    out = torch.empty_like(inp)
+    ops.unary("gelu_tanh", inp, out)
+    assert torch.allclose(out, torch.nn.GELU(approximate="tanh")(inp), rtol=1e-4, atol=1e-3)
+
+
+def test_softmax_torch_case():
+    from hexb200 import ops
+    inp = torch.rand(128, 128, dtype=torch.float16)
+    out = torch.empty_like(inp)
+    ops.softmax(inp, out)
+    assert torch.allclose(out, torch.nn.Softmax(dim=1)(inp.float()).half(), rtol=1e-3, atol=1e-3)
+
+
+def test_layernorm_torch_case():
+    from hexb200 import ops
+    model = torch.nn.LayerNorm(normalized_shape=128)
+    inp = torch.rand(128, 128, dtype=torch.float16)
+    out = torch.empty_like(inp)
+    ops.layer_norm(inp, out, model.weight.detach().half(), model.bias.detach().half(), eps=model.eps)
+    ref = model(inp.float()).half()
+    assert torch.allclose(out, ref, rtol=5e-1, atol=1e-2)          # the reference's own (loose) bound
+    assert torch.allclose(out, ref, rtol=1e-2, atol=2e-3)          # what this kernel actually holds
