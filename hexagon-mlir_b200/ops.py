@@ -163,6 +163,8 @@ def matmul_nt(a, bt, c, residual=None) -> None:
     """c = a @ bt.T for a [M, K], bt [N, K] (a weight stored transposed), float16 CUDA tensors; c float16 or
     float32.  Reference: test/python/torch-mlir/test_hexkl_macro_matmul.py:24-28,51-69."""
     lib = _lib.load()
+    if any(t is not None and t.device.type != "cuda" for t in (a, bt, c, residual)):
+        return _stage(lambda a, bt, c, residual: matmul_nt(a, bt, c, residual), dict(a=a, bt=bt, c=c, residual=residual), ("c",))
     _same_place(a, bt, c, residual)
     if a.dtype != torch.float16 or bt.dtype != torch.float16:
         raise TypeError("matmul_nt: A and Bt must be float16")
@@ -184,6 +186,11 @@ def linear(a, w, c, bias=None, residual=None, act: str = "none", w_transposed: b
     act: "none" or "gelu_tanh".  Reference: the addmm / gelu / add chains of the GPT-2 graph,
     test/python/torch-mlir/gpt2lmheadmodel.py:143-169."""
     lib = _lib.load()
+    if any(t is not None and t.device.type != "cuda" for t in (a, w, c, bias, residual)):
+        res_is_c = residual is c
+        tensors = dict(a=a, w=w, c=c, bias=bias, residual=None if res_is_c else residual)
+        return _stage(lambda a, w, c, bias, residual: linear(a, w, c, bias, c if res_is_c else residual, act, w_transposed),
+                      tensors, ("c",))
     _same_place(a, w, c, bias, residual)
     if a.dtype != torch.float16 or w.dtype != torch.float16:
         raise TypeError("linear: A and W must be float16")
@@ -211,6 +218,9 @@ def linear(a, w, c, bias=None, residual=None, act: str = "none", w_transposed: b
 def embedding(wte, wpe, ids, out) -> None:
     """out[b, s, :] = wte[ids[b, s], :] + wpe[s, :] for float16 tables and int64 ids [batch, seq]."""
     lib = _lib.load()
+    if any(t.device.type != "cuda" for t in (wte, wpe, ids, out)):
+        return _stage(lambda wte, wpe, ids, out: embedding(wte, wpe, ids, out), dict(wte=wte, wpe=wpe, ids=ids, out=out),
+                      ("out",))
     _same_place(wte, wpe, ids, out)
     if wte.dtype != torch.float16 or wpe.dtype != torch.float16 or out.dtype != torch.float16:
         raise TypeError("embedding: tables and output must be float16")
@@ -296,9 +306,10 @@ def attention_ex(q, k, v, out, mask=None, sm_scale=None, causal: bool = False) -
     (qcom_hexagon_backend/lib/Transforms/LowerTmTensor.cpp:126-160).
     """
     lib = _lib.load()
+    if any(t is not None and t.device.type != "cuda" for t in (q, k, v, out, mask)):
+        return _stage(lambda q, k, v, out, mask: attention_ex(q, k, v, out, mask, sm_scale, causal),
+                      dict(q=q, k=k, v=v, out=out, mask=mask), ("out",))
     dev = _same_place(q, k, v, out, mask)
-    if dev.type != "cuda":
-        raise ValueError("attention_ex: CUDA tensors only")
     if not (q.dim() == k.dim() == v.dim() == out.dim() == 4):
         raise ValueError("attention_ex: expected [Z, H, N, D] tensors")
     Z, H, NQ, D = q.shape
@@ -385,6 +396,19 @@ def _on_device(*ts):
     return host, [t.cuda() if host else t for t in ts]
 
 
+def _stage(fn, tensors: dict, outputs: tuple):
+    """Runs fn(**tensors) with every CPU tensor staged through the current CUDA device (torch moves the
+    bytes, nothing else) and copies the tensors named in `outputs` back; CUDA tensors pass through."""
+    host = any(t is not None and t.device.type != "cuda" for t in tensors.values())
+    if not host:
+        return fn(**tensors)
+    staged = {k: (None if t is None else (t.cuda() if t.device.type != "cuda" else t)) for k, t in tensors.items()}
+    fn(**staged)
+    for k in outputs:
+        if tensors[k].device.type != "cuda":
+            tensors[k].copy_(staged[k])
+
+
 def unary(op: str, x, out) -> None:
     """out = op(x), op in gelu_tanh / cos / sin / rsqrt (reference: test_gelu.py:25-54,
     test_math_ops.py:24-37, test_rsqrt.py:19-24)."""
@@ -449,9 +473,9 @@ def cumsum(x, out, axis: int = -1, reverse: bool = False) -> None:
     of float32, float16 (fp32 accumulation) or int32.  Reference: ttx.cumsum / ttx.scan with an addition body
     (qcom_hexagon_backend/include/hexagon/Dialect/TTX/IR/TTXOps.td:25-75, lib/Transforms/LowerTTX.cpp:75-300)."""
     lib = _lib.load()
+    if x.device.type != "cuda" or out.device.type != "cuda":
+        return _stage(lambda x, out: cumsum(x, out, axis, reverse), dict(x=x, out=out), ("out",))
     dev = _same_place(x, out)
-    if dev.type != "cuda":
-        raise ValueError("cumsum: CUDA tensors only")
     if x.shape != out.shape or x.dtype != out.dtype or not (x.is_contiguous() and out.is_contiguous()):
         raise ValueError("cumsum: x and out must be contiguous with equal shape and dtype")
     if x.dim() == 0:

@@ -179,3 +179,30 @@ def test_empty_and_degenerate_inputs_of_the_newer_entry_points():
     ops.iota(torch.empty(0, device=dev))
     assert hexb200.device_status() == 0
     assert lib.hexb_cumsum(99, None, None, 1, 1, 1, 0, None) != 0          # unknown dtype
+
+
+def test_newer_ops_accept_host_tensors():
+    """CPU tensors are staged through the device and the results written back in place, as the reference's
+    launchers take CPU tensors (backend/triton_hexagon_launcher.py:716-728)."""
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(64, 32, generator=g).half()
+    w = torch.randn(32, 48, generator=g).half()
+    bias = torch.randn(48, generator=g).half()
+    c = torch.empty(64, 48, dtype=torch.float16)
+    ops.linear(a, w, c, bias=bias, act="gelu_tanh")
+    ref = a.float() @ w.float() + bias.float()
+    ref = 0.5 * ref * (1 + torch.tanh(0.797885 * ref + 0.035677 * ref ** 3))
+    assert O.max_rel_err(c, ref) < 2e-2
+    c2 = torch.empty(64, 48, dtype=torch.float32)
+    ops.matmul_nt(a, w.T.contiguous(), c2)
+    assert O.max_rel_err(c2, a.float() @ w.float()) < 2e-3
+    x = torch.randint(-50, 50, (5, 1000), generator=g, dtype=torch.int32)
+    y = torch.empty_like(x)
+    ops.cumsum(x, y, axis=1)
+    assert torch.equal(y, x.cumsum(1).to(torch.int32))
+    q, k, v = (torch.randn(1, 2, 96, 64, generator=g).half() for _ in range(3))
+    mask = torch.randn(96, 96, generator=g).half()
+    o = torch.empty_like(q)
+    ops.attention_ex(q, k, v, o, mask=mask)
+    s = q.float() @ k.float().transpose(-1, -2) / 8.0 + mask.float()
+    assert O.max_rel_err(o, torch.softmax(s, -1) @ v.float()) < 2e-2
