@@ -55,3 +55,81 @@ def all_gather_rows(local: torch.Tensor, total_rows: int, group=None) -> torch.T
     buf = local.new_empty((world * mx,) + tuple(local.shape[1:]))
     dist.all_gather_into_tensor(buf, padded, group=group)
     return torch.cat([buf[r * mx: r * mx + counts[r]] for r in range(world)], dim=0)
+
+
+# ------------------------------------------------------------------ the five configurations, partitioned
+# name -> (unit, operands cut along their leading units, operands every rank holds whole).
+# Attention tensors [Z, H, N, D] are cut in (batch, head) pairs, i.e. along dimension 0 of their
+# [Z*H, N, D] view; everything else is cut along dimension 0 as stored.
+PARTITIONS = {
+    "softmax": ("row", ("x",), ()),
+    "layernorm": ("row", ("x",), ("weight", "bias")),
+    "gemm": ("row of A", ("a",), ("b",)),
+    "attention": ("(batch, head) pair", ("q", "k", "v"), ()),
+    "decoder": ("sequence", ("x",), ("weights",)),
+}
+
+
+def _units_view(name: str, t: torch.Tensor) -> torch.Tensor:
+    """The tensor with its partition units along dimension 0."""
+    if name == "attention":
+        if t.dim() != 4:
+            raise ValueError("attention operands are [Z, H, N, D]")
+        return t.reshape(t.shape[0] * t.shape[1], t.shape[2], t.shape[3])
+    return t
+
+
+def partition(name: str, inputs: dict, world_size: int, rank: int) -> dict:
+    """The operands rank ``rank`` works on: its block of every cut operand (a view, no copy),
+    the replicated operands untouched.  ``inputs`` maps operand names of PARTITIONS[name] to tensors."""
+    _, cut, whole = PARTITIONS[name]
+    missing = [k for k in cut + whole if k not in inputs]
+    if missing:
+        raise KeyError(f"{name}: missing operands {missing}")
+    out = {k: inputs[k] for k in whole}
+    for k in cut:
+        out[k] = shard_rows(_units_view(name, inputs[k]), world_size, rank)
+    return out
+
+
+def units_of(name: str, inputs: dict) -> int:
+    """Number of independent units (rows, (batch, head) pairs, sequences) in the whole problem."""
+    return _units_view(name, inputs[PARTITIONS[name][1][0]]).shape[0]
+
+
+def run_partitioned(name: str, inputs: dict, compute, world_size: int, rank: int, group=None, gather: bool = True):
+    """Shard -> compute -> gather for one configuration.
+
+    ``compute(**local_operands)`` returns the rank's block of the output with the units along
+    dimension 0 (for attention: [pairs, N, D]).  With ``gather`` the blocks of all ranks are
+    all-gathered and every rank returns the whole output; otherwise the local block is returned.
+    The benchmark's multi-GPU leg and the two-rank CPU test both go through this function.
+    """
+    local = partition(name, inputs, world_size, rank)
+    y_local = compute(**local)
+    total = units_of(name, inputs)
+    want = shard_range(total, world_size, rank)[1]
+    if y_local.shape[0] != want:
+        raise ValueError(f"{name}: compute returned {y_local.shape[0]} units, the partition gives rank {rank} {want}")
+    if not gather:
+        return y_local
+    y = all_gather_rows(y_local, total, group=group)
+    if name == "attention":
+        q = inputs["q"]
+        y = y.reshape(q.shape[0], q.shape[1], y.shape[1], y.shape[2])
+    return y
+
+
+def sample_units(total: int, world_size: int, per_rank: int = 2) -> list:
+    """Unit indices for a spot check of a gathered output: the first and last unit of every rank's
+    block (plus evenly spaced ones up to ``per_rank``), so that a misplaced or missing shard of any
+    rank shows up."""
+    picks = set()
+    for r in range(world_size):
+        s, c = shard_range(total, world_size, r)
+        if c == 0:
+            continue
+        n = min(per_rank, c)
+        for i in range(n):
+            picks.add(s + (i * (c - 1)) // max(n - 1, 1))
+    return sorted(picks)

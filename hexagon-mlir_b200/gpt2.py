@@ -89,8 +89,8 @@ class GPT2Runner:
         """Kernel launches of one forward pass (embedding + blocks + final norm + LM head)."""
         return 1 + self.LAUNCHES_PER_LAYER * self.cfg.n_layer + 2
 
-    def _buffers(self, B: int, S: int, logits_dtype):
-        key = (B, S, logits_dtype)
+    def _buffers(self, B: int, S: int, logits_dtype, last_only: bool = False):
+        key = (B, S, logits_dtype, last_only)
         if key not in self._bufs:
             d, dev, h = self.cfg.n_embd, self.device, torch.float16
             T = B * S
@@ -98,8 +98,10 @@ class GPT2Runner:
                 "x": torch.empty(T, d, dtype=h, device=dev), "x2": torch.empty(T, d, dtype=h, device=dev),
                 "ln": torch.empty(T, d, dtype=h, device=dev), "qkv": torch.empty(T, 3 * d, dtype=h, device=dev),
                 "att": torch.empty(T, d, dtype=h, device=dev), "fc": torch.empty(T, 4 * d, dtype=h, device=dev),
-                # rows padded to a multiple of 16 bytes so that the LM head stores whole vectors
-                "logits": torch.empty(T, (self.cfg.vocab_size + 7) // 8 * 8, dtype=logits_dtype, device=dev),
+                # rows padded to a multiple of 16 bytes so that the LM head stores whole vectors; one row per
+                # sequence when only the last position is asked for
+                "logits": torch.empty(B if last_only else T, (self.cfg.vocab_size + 7) // 8 * 8, dtype=logits_dtype,
+                                      device=dev),
             }
         return self._bufs[key]
 
@@ -140,7 +142,7 @@ class GPT2Runner:
         cfg, w = self.cfg, self.w
         B, S = input_ids.shape
         d, H, D = cfg.n_embd, cfg.n_head, self.head_dim
-        b = self._buffers(B, S, logits_dtype)
+        b = self._buffers(B, S, logits_dtype, last_only)
         x, x2 = b["x"], b["x2"]
         ops.embedding(w["transformer.wte.weight"], w["transformer.wpe.weight"], input_ids, x.view(B, S, d))
         qkv4 = b["qkv"].view(B, S, 3, H, D)

@@ -8,8 +8,8 @@ Two layers, both CPU-only:
                  test_rms_norm.py:85-87, test_matmul.py:90, test_flash_attention.py:212), computed in
                  fp32 from the fp16 inputs where the data is fp16, so that a tolerance measures the
                  kernel and not the comparator.
-plus the seeded input generators for the five benchmark configurations.  Only tests/, the smoke
-check and the cpu_baseline / reference arm of bench.py import this module.
+Only tests/, the smoke check and the CPU legs of bench.py (cpu_baseline, the reference arm, and the
+untimed comparison of gathered multi-GPU output) import this module.
 
 Parity status: pinned against torch CPU and against outputs of the reference's own Triton kernels
 executed in Triton's interpreter (tests/golden/*.npz, made by tests/golden/make_golden.py).  Parity
@@ -253,7 +253,6 @@ def torch_decoder(x, weights, n_heads, head_dim, d_ff, batch, seq, eps, store_dt
     return cur.to(x.dtype).reshape(x.shape)
 
 
-# ------------------------------------------------------------------ seeded inputs of the five configurations
 def torch_gpt2(sd, n_layer, n_head, eps, input_ids):
     """GPT2LMHeadModel forward in plain fp32 torch from a Hugging Face state dict: what the reference runs
     on x86 as its expected result (test/python/torch-mlir/gpt2lmheadmodel.py:30-33, 143-169).  Conv1D is
@@ -281,48 +280,11 @@ def torch_gpt2(sd, n_layer, n_head, eps, input_ids):
     return x @ f["transformer.wte.weight"].T
 
 
-def _gen(seed):
-    return torch.Generator(device="cpu").manual_seed(seed)
-
-
-def make_softmax_inputs(rows=8192, cols=1024, dtype=torch.float32, seed=1001):
-    return torch.randn(rows, cols, generator=_gen(seed)).to(dtype)
-
-
-def make_layer_norm_inputs(rows=16384, cols=4096, dtype=torch.float16, seed=1002):
-    g = _gen(seed)
-    x = torch.randn(rows, cols, generator=g).to(dtype)
-    w = (0.5 + torch.rand(cols, generator=g)).to(dtype)
-    b = (-0.1 + 0.2 * torch.rand(cols, generator=g)).to(dtype)
-    return x, w, b
-
-
-def make_matmul_inputs(M=4096, N=4096, K=4096, seed=1003):
-    g = _gen(seed)
-    a = (2 * torch.rand(M, K, generator=g) - 1).to(torch.float16)
-    b = (2 * torch.rand(K, N, generator=g) - 1).to(torch.float16)
-    return a, b
-
-
-def make_attention_inputs(Z=4, H=32, N=4096, D=128, dtype=torch.float16, seed=1004):
-    g = _gen(seed)
-    s = D ** -0.5
-    return tuple((torch.randn(Z, H, N, D, generator=g) * s).to(dtype) for _ in range(3))
-
-
-def make_decoder_inputs(n_layers=4, d_model=2048, n_heads=16, d_ff=8192, batch=8, seq=1024, seed=1005):
-    g = _gen(seed)
-    x = (0.02 * torch.randn(batch, seq, d_model, generator=g)).to(torch.float16)
-    weights = []
-    for layer in range(n_layers):
-        gl = _gen(seed + 1 + layer)
-        mk = lambda r, c: (torch.randn(r, c, generator=gl) * r ** -0.5).to(torch.float16)
-        weights.append({
-            "wqkv": mk(d_model, 3 * d_model), "wo": mk(d_model, d_model), "wgu": mk(d_model, 2 * d_ff),
-            "wd": mk(d_ff, d_model), "g1": torch.ones(d_model, dtype=torch.float16),
-            "g2": torch.ones(d_model, dtype=torch.float16),
-        })
-    return x, weights
+# ------------------------------------------------------------------ seeded inputs of the five configurations
+# The seeded generators live in the product package (hexb200.synth) so that the benchmark's GPU arm
+# needs nothing from this directory; they are re-exported here for the tests.
+from hexb200.synth import (make_attention_inputs, make_decoder_inputs, make_layer_norm_inputs,  # noqa: E402,F401
+                           make_matmul_inputs, make_softmax_inputs)
 
 
 def max_rel_err(got: torch.Tensor, ref: torch.Tensor) -> float:
