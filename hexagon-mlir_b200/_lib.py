@@ -14,6 +14,7 @@ LIB_PATH = HERE / "libhexb200.so"
 HEXB_OK = 0
 HEXB_DT_F16 = 1
 HEXB_DT_F32 = 2
+HEXB_DT_I32 = 6   # the reference's raw-tensor id of Int32 (test/utils/dsp/include/tensor.h:26-38)
 
 
 class HexbError(RuntimeError):
@@ -56,6 +57,7 @@ PROTOTYPES = {
     "hexb_status_string": (C.c_char_p, [_i]),
     "hexb_last_cuda_error": (C.c_char_p, []),
     "hexb_device_status": (_i, [C.POINTER(_i)]),
+    "hexb_selftest_bounded_wait": (_i, [_i, _vp]),
     "hexb_softmax_f32": (_i, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "hexb_softmax_f16": (_i, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "hexb_layer_norm_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f, _vp]),

@@ -7,9 +7,8 @@
 // back; here the crossing is a pair of PCIe copies around an in-process launch.
 #include <cstdio>
 #include <cstring>
-#include <map>
+#include <atomic>
 #include <mutex>
-#include <string>
 
 #include "common.cuh"
 
@@ -32,22 +31,33 @@ int check_launch(const char *where) {
 }
 
 static std::mutex g_mu;
-static std::map<std::string, int> &options() {
-  static std::map<std::string, int> m;
-  return m;
+
+// ---- option store: one atomic word per option (bit 32 = "has been set", low 32 bits = value)
+static std::atomic<int64_t> g_opt[OPT_COUNT];
+static const char *const kOptName[OPT_COUNT] = {
+#define HEXB_X(n) #n,
+    HEXB_OPTIONS(HEXB_X) HEXB_DEV_OPTIONS(HEXB_X)
+#undef HEXB_X
+};
+#define HEXB_X(n) +1
+static constexpr int kShippedOptions = 0 HEXB_OPTIONS(HEXB_X);  // the dev-only names follow these
+#undef HEXB_X
+
+int option(Opt key, int dflt) {
+  const int64_t v = g_opt[key].load(std::memory_order_relaxed);
+  return (v >> 32) & 1 ? (int)(uint32_t)v : dflt;
 }
 
-int option(const char *key, int dflt) {
-  std::lock_guard<std::mutex> lk(g_mu);
-  auto it = options().find(key);
-  return it == options().end() ? dflt : it->second;
+static int find_option(const char *key) {
+#ifdef HEXB_DEV
+  const int n = OPT_COUNT;
+#else
+  const int n = kShippedOptions;
+#endif
+  for (int i = 0; i < n; ++i)
+    if (!strcmp(kOptName[i], key)) return i;
+  return -1;
 }
-
-static const char *kKnownOptions[] = {
-    "softmax_vpt_max", "softmax_force_stream", "softmax_ring", "softmax_bulk_store", "norm_ring", "norm_bulk_store", "ring_bytes_per_warp", "ring_map", "ring_dbg", "norm_vpt_max", "norm_force_stream",
-    "norm_ctas_per_sm", "gemm_bn", "gemm_b_lbo", "gemm_b_sbo", "gemm_tail_split", "gemm_pair", "gemm_epi_warps", "gemm_tma_store", "gemm_force_simt", "attn_force_simt",
-    "attn_v_lbo", "attn_v_sbo", "attn_tiles_per_cta", "attn_kernel", "attn_mask_tma", "scan_force_scalar", "scan_segments", "scan_kv", "decoder_fused_swiglu",
-    "host_chunks", "pdl", nullptr};
 
 int current_device(DeviceInfo *out) {
   static DeviceInfo cache[64];
@@ -82,6 +92,7 @@ int scratch_alloc(void **ptr, size_t bytes, cudaStream_t st) {
   int dev = 0;
   HEXB_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return HEXB_ERR_NO_DEVICE;
+  cudaMemPool_t mine = nullptr;
   {
     std::lock_guard<std::mutex> lk(g_mu);
     if (!pools[dev]) {
@@ -96,8 +107,9 @@ int scratch_alloc(void **ptr, size_t bytes, cudaStream_t st) {
       HEXB_CUDA_OK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
       pools[dev] = pool;
     }
+    mine = pools[dev];
   }
-  HEXB_CUDA_OK(cudaMallocFromPoolAsync(ptr, bytes, pools[dev], st));
+  HEXB_CUDA_OK(cudaMallocFromPoolAsync(ptr, bytes, mine, st));
   return HEXB_OK;
 }
 
@@ -148,7 +160,20 @@ static inline size_t dt_size(int dt) { return dt == HEXB_DT_F16 ? 2 : dt == HEXB
 // and the download of chunk i-1 overlap (PCIe is full duplex and each direction has its own copy
 // engine).  `launch(x_dev, y_dev, extra_dev, row0, nrows, stream)`; a call with x_dev == nullptr
 // uploads the operator's small operands (gains, biases), one with nrows == -1 downloads its small
-// results (statistics) after the last chunk.
+// results (statistics) after the last chunk.  The overlap needs page-locked host buffers
+// (cudaHostAlloc / cudaHostRegister, torch's pin_memory()): with pageable memory the runtime stages
+// every copy through its own bounce buffer and the device-to-host copies block the calling thread,
+// so the chunks run one after the other (the results are the same).
+// Waits for everything queued on the staging streams.  Every `_host` entry point calls this before it
+// returns an error: copies against the caller's host buffers must not still be in flight when the
+// caller gets control back (it may free them), nor when the next call reuses the staging block.
+static void staging_drain(Staging *s) {
+  if (!s) return;
+  for (auto &st : s->streams)
+    if (st) cudaStreamSynchronize(st);
+  cudaGetLastError();
+}
+
 template <typename F>
 static int rows_pipeline(const void *x, void *y, int64_t rows, int64_t cols, size_t esz,
                          size_t extra_bytes, F &&launch_with_extra) {
@@ -161,32 +186,37 @@ static int rows_pipeline(const void *x, void *y, int64_t rows, int64_t cols, siz
   Staging *s = nullptr;
   if (int st = staging_get(2 * mat + extra, &s)) return st;
   char *dx = (char *)s->ptr, *dy = dx + mat, *de = dy + mat;
-  int chunks = option("host_chunks", 8);
+  int chunks = option(OPT_host_chunks, 8);
   if (chunks < 1) chunks = 1;
   if (chunks > Staging::kMaxChunks) chunks = Staging::kMaxChunks;
   if ((int64_t)chunks > rows) chunks = (int)rows;
   if ((size_t)rows * row_bytes < ((size_t)4 << 20)) chunks = 1;
   cudaStream_t s_in = s->streams[0], s_k = s->streams[1], s_out = s->streams[2];
-  if (int st = launch_with_extra(nullptr, nullptr, de, 0, 0, s_in)) return st;  // small operands
-  const int64_t per = (rows + chunks - 1) / chunks;
-  for (int c = 0; c < chunks; ++c) {
-    const int64_t r0 = (int64_t)c * per;
-    const int64_t nr = rows - r0 < per ? rows - r0 : per;
-    if (nr <= 0) break;
-    const size_t off = (size_t)r0 * row_bytes;
-    HEXB_CUDA_OK(cudaMemcpyAsync(dx + off, (const char *)x + off, (size_t)nr * row_bytes,
-                                 cudaMemcpyHostToDevice, s_in));
-    HEXB_CUDA_OK(cudaEventRecord(s->ev_in[c], s_in));
-    HEXB_CUDA_OK(cudaStreamWaitEvent(s_k, s->ev_in[c], 0));
-    if (int e = launch_with_extra(dx + off, dy + off, de, r0, nr, s_k)) return e;
-    HEXB_CUDA_OK(cudaEventRecord(s->ev_k[c], s_k));
-    HEXB_CUDA_OK(cudaStreamWaitEvent(s_out, s->ev_k[c], 0));
-    HEXB_CUDA_OK(cudaMemcpyAsync((char *)y + off, dy + off, (size_t)nr * row_bytes,
-                                 cudaMemcpyDeviceToHost, s_out));
-  }
-  if (int st = launch_with_extra(dx, dy, de, 0, -1, s_out)) return st;  // small results
-  HEXB_CUDA_OK(cudaStreamSynchronize(s_out));
-  return HEXB_OK;
+  auto body = [&]() -> int {
+    if (int st = launch_with_extra(nullptr, nullptr, de, 0, 0, s_in)) return st;  // small operands
+    const int64_t per = (rows + chunks - 1) / chunks;
+    for (int c = 0; c < chunks; ++c) {
+      const int64_t r0 = (int64_t)c * per;
+      const int64_t nr = rows - r0 < per ? rows - r0 : per;
+      if (nr <= 0) break;
+      const size_t off = (size_t)r0 * row_bytes;
+      HEXB_CUDA_OK(cudaMemcpyAsync(dx + off, (const char *)x + off, (size_t)nr * row_bytes,
+                                   cudaMemcpyHostToDevice, s_in));
+      HEXB_CUDA_OK(cudaEventRecord(s->ev_in[c], s_in));
+      HEXB_CUDA_OK(cudaStreamWaitEvent(s_k, s->ev_in[c], 0));
+      if (int e = launch_with_extra(dx + off, dy + off, de, r0, nr, s_k)) return e;
+      HEXB_CUDA_OK(cudaEventRecord(s->ev_k[c], s_k));
+      HEXB_CUDA_OK(cudaStreamWaitEvent(s_out, s->ev_k[c], 0));
+      HEXB_CUDA_OK(cudaMemcpyAsync((char *)y + off, dy + off, (size_t)nr * row_bytes,
+                                   cudaMemcpyDeviceToHost, s_out));
+    }
+    if (int st = launch_with_extra(dx, dy, de, 0, -1, s_out)) return st;  // small results
+    HEXB_CUDA_OK(cudaStreamSynchronize(s_out));
+    return HEXB_OK;
+  };
+  const int status = body();
+  if (status != HEXB_OK) staging_drain(s);
+  return status;
 }
 
 }  // namespace hexb
@@ -213,21 +243,19 @@ extern "C" const char *hexb_last_cuda_error(void) { return g_err_text; }
 
 extern "C" int hexb_set_option(const char *key, int value) {
   if (!key) return HEXB_ERR_BAD_ARG;
-  for (const char **k = kKnownOptions; *k; ++k)
-    if (!strcmp(*k, key)) {
-      std::lock_guard<std::mutex> lk(g_mu);
-      options()[key] = value;
-      return HEXB_OK;
-    }
-  return HEXB_ERR_BAD_ARG;
+  const int i = find_option(key);
+  if (i < 0) return HEXB_ERR_BAD_ARG;
+  g_opt[i].store(((int64_t)1 << 32) | (uint32_t)value, std::memory_order_relaxed);
+  return HEXB_OK;
 }
 
 extern "C" int hexb_get_option(const char *key, int *value) {
   if (!key || !value) return HEXB_ERR_BAD_ARG;
-  std::lock_guard<std::mutex> lk(g_mu);
-  auto it = options().find(key);
-  if (it == options().end()) return HEXB_ERR_BAD_ARG;
-  *value = it->second;
+  const int i = find_option(key);
+  if (i < 0) return HEXB_ERR_BAD_ARG;
+  const int64_t v = g_opt[i].load(std::memory_order_relaxed);
+  if (!((v >> 32) & 1)) return HEXB_ERR_BAD_ARG;  // never set: the launchers use their own defaults
+  *value = (int)(uint32_t)v;
   return HEXB_OK;
 }
 
@@ -321,15 +349,39 @@ extern "C" int hexb_matmul_f16_host(const void *A, const void *B, void *C, int64
   Staging *s = nullptr;
   if (int st = staging_get(ab + bb + cb, &s)) return st;
   char *dA = (char *)s->ptr, *dB = dA + ab, *dC = dB + bb;
-  cudaStream_t st = s->streams[0];
-  if (K > 0) {
-    HEXB_CUDA_OK(cudaMemcpyAsync(dA, A, (size_t)M * K * 2, cudaMemcpyHostToDevice, st));
-    HEXB_CUDA_OK(cudaMemcpyAsync(dB, B, (size_t)K * N * 2, cudaMemcpyHostToDevice, st));
-  }
-  if (int e = hexb_matmul_f16(dA, dB, dC, nullptr, M, N, K, K, N, N, out_dtype, st)) return e;
-  HEXB_CUDA_OK(cudaMemcpyAsync(C, dC, (size_t)M * N * osz, cudaMemcpyDeviceToHost, st));
-  HEXB_CUDA_OK(cudaStreamSynchronize(st));
-  return HEXB_OK;
+  cudaStream_t s_in = s->streams[0], s_k = s->streams[1], s_out = s->streams[2];
+  // B is needed whole by every row block; A goes up and C comes back in blocks of rows (multiples of
+  // 256, the tile height of the CTA-pair kernel) so that the upload of block i+1, the product of
+  // block i and the download of block i-1 overlap.
+  int chunks = option(OPT_host_chunks, 8);
+  if (chunks > Staging::kMaxChunks) chunks = Staging::kMaxChunks;
+  int64_t per = chunks > 1 ? (M + chunks - 1) / chunks : M;
+  per = (per + 255) / 256 * 256;
+  if ((size_t)M * K * 2 < ((size_t)4 << 20) || per >= M) per = M;
+  auto body = [&]() -> int {
+    if (K > 0) HEXB_CUDA_OK(cudaMemcpyAsync(dB, B, (size_t)K * N * 2, cudaMemcpyHostToDevice, s_in));
+    int c = 0;
+    for (int64_t r0 = 0; r0 < M; r0 += per, ++c) {
+      const int64_t nr = M - r0 < per ? M - r0 : per;
+      if (K > 0)
+        HEXB_CUDA_OK(cudaMemcpyAsync(dA + (size_t)r0 * K * 2, (const char *)A + (size_t)r0 * K * 2, (size_t)nr * K * 2,
+                                     cudaMemcpyHostToDevice, s_in));
+      HEXB_CUDA_OK(cudaEventRecord(s->ev_in[c], s_in));
+      HEXB_CUDA_OK(cudaStreamWaitEvent(s_k, s->ev_in[c], 0));
+      if (int e = hexb_matmul_f16(dA + (size_t)r0 * K * 2, dB, dC + (size_t)r0 * N * osz, nullptr, nr, N, K, K, N, N,
+                                  out_dtype, s_k))
+        return e;
+      HEXB_CUDA_OK(cudaEventRecord(s->ev_k[c], s_k));
+      HEXB_CUDA_OK(cudaStreamWaitEvent(s_out, s->ev_k[c], 0));
+      HEXB_CUDA_OK(cudaMemcpyAsync((char *)C + (size_t)r0 * N * osz, dC + (size_t)r0 * N * osz, (size_t)nr * N * osz,
+                                   cudaMemcpyDeviceToHost, s_out));
+    }
+    HEXB_CUDA_OK(cudaStreamSynchronize(s_out));
+    return HEXB_OK;
+  };
+  const int status = body();
+  if (status != HEXB_OK) staging_drain(s);
+  return status;
 }
 
 extern "C" int hexb_attention_fwd_host(int dtype, const void *Q, const void *K, const void *V,
@@ -349,6 +401,7 @@ extern "C" int hexb_attention_fwd_host(int dtype, const void *Q, const void *K, 
   char *dq = (char *)s->ptr, *dk = dq + tb, *dv = dk + tb, *dout = dv + tb;
   const int64_t sz = H * N_CTX * D, sh = N_CTX * D, sn = D;
   const int64_t strides[12] = {sz, sh, sn, sz, sh, sn, sz, sh, sn, sz, sh, sn};
+  auto body = [&]() -> int {
   for (int64_t z = 0; z < Z; ++z) {
     cudaStream_t st = s->streams[z % 3];
     const size_t off = (size_t)z * per_z;
@@ -366,4 +419,8 @@ extern "C" int hexb_attention_fwd_host(int dtype, const void *Q, const void *K, 
   }
   for (auto &st : s->streams) HEXB_CUDA_OK(cudaStreamSynchronize(st));
   return HEXB_OK;
+  };
+  const int status = body();
+  if (status != HEXB_OK) staging_drain(s);
+  return status;
 }

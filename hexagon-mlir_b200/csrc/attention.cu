@@ -469,7 +469,8 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   auto v_full = [&](uint32_t b) { return bar0 + 72 + 8 * b; };
   auto v_empty = [&](uint32_t b) { return bar0 + 88 + 8 * b; };
   auto s_full = [&](uint32_t b) { return bar0 + 104 + 8 * b; };
-  // p_full[2] follow at +120 (NBAR = 15 counts q_full..s_full; two more for p_full)
+  // barrier slots: q_full .. pv_done (5), then pairs k_full, k_empty, v_full, v_empty, s_full, p_full (12), then
+  // one m_full per softmax warp (4): NBAR = 21
   auto p_full = [&](uint32_t b) { return bar0 + 120 + 8 * b; };
   auto m_full = [&](uint32_t w) { return bar0 + 136 + 8 * w; };   // one per softmax warp
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + 168);
@@ -901,7 +902,10 @@ attn_fwd_simt_kernel(const T *__restrict__ Q, const T *__restrict__ K, const T *
       }
     }
     const float m_raw = fmaxf(m, warp_max(s));
-    const float m_new = m_raw == -INFINITY ? 0.f : m_raw;  // every key so far masked out: weights 0, not NaN
+    // every key so far masked out: this step's weights are 0, not NaN.  A row whose keys are ALL masked
+    // ends with l == 0 and the final acc * (1 / l) = 0 * inf is NaN, as on the tensor-core path and as the
+    // reference's exp(-inf - -inf).
+    const float m_new = m_raw == -INFINITY ? 0.f : m_raw;
     const float pe = (kv < kv_end) ? exp2f(s - m_new) : 0.f;
     const float alpha = exp2f(m - m_new);  // m == -inf on the first step: alpha = 0, acc and l are 0
     l = l * alpha + warp_sum(pe);
@@ -967,7 +971,7 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   using cfg = Cfg<HD>;
   // 2: 64-key blocks, two score buffers; 1: 128-key blocks (plain calls only)
   const bool plain = !x.mask && !x.out_f32 && x.n_kv == N;
-  const int which = (int)option("attn_kernel", 2);
+  const int which = (int)option(OPT_attn_kernel, 2);
   const bool two_buffers = !plain || which != 1;
   const bool wide = two_buffers && !x.mask && which == 5;  // 128-key blocks, one CTA per SM
   CUtensorMap tm[4];
@@ -979,10 +983,10 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
     const uint32_t box[4] = {64, (i > 0 && two_buffers && !wide) ? 64u : 128u, 1, 1};  // rows per K/V load
     if (int e = encode_tmap_f16_sw128(&tm[i], base[i], 4, dims, strides, box)) return e;
   }
-  static bool attr_done[64] = {};
+  static PerDeviceOnce attr_done;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_done[dev & 63]) {
+  if (!attr_done.is_done(dev)) {
     HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
     HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg2<HD>::SMEM_BYTES));
@@ -990,7 +994,7 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
                                       Cfg2<HD>::SMEM_BYTES_MASK));
     HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg2<HD, 128>::SMEM_BYTES));
-    attr_done[dev & 63] = true;
+    attr_done.mark(dev);
   }
   Params p;
 #ifdef HEXB_ATTN_PROFILE
@@ -1010,7 +1014,7 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   }
   p.mask_h_on = x.sm[1] != 0;
   p.mask_z_on = x.sm[0] != 0;
-  p.mask_tma = p.mask_vec_ok && !x.mask_f32 && x.sm[2] >= x.n_kv && option("attn_mask_tma", 1);
+  p.mask_tma = p.mask_vec_ok && !x.mask_f32 && x.sm[2] >= x.n_kv && option(OPT_attn_mask_tma, 1);
   tm[3] = tm[0];
   if (p.mask_tma) {
     // a broadcast dimension becomes an extent of 1 (its stride is then never applied)
@@ -1032,10 +1036,10 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
     const int per16 = x.out_f32 ? 4 : 8;
     p.out_vec_ok = aligned16(O) && s[9] % per16 == 0 && s[10] % per16 == 0 && s[11] % per16 == 0;
   }
-  p.v_lbo = (uint32_t)option("attn_v_lbo", cfg::CHUNK_BYTES);
-  p.v_sbo = (uint32_t)option("attn_v_sbo", 1024);
+  p.v_lbo = (uint32_t)HEXB_DEV_OPTION(OPT_attn_v_lbo, cfg::CHUNK_BYTES);
+  p.v_sbo = (uint32_t)HEXB_DEV_OPTION(OPT_attn_v_sbo, 1024);
   // pairing pays when the tiles differ in length (causal); equal tiles run slightly faster one per CTA
-  p.tiles_per_cta = (p.num_q_tiles % 2 == 0 && option("attn_tiles_per_cta", causal ? 2 : 1) == 2) ? 2 : 1;
+  p.tiles_per_cta = (p.num_q_tiles % 2 == 0 && option(OPT_attn_tiles_per_cta, causal ? 2 : 1) == 2) ? 2 : 1;
   p.ctas_per_bh = p.num_q_tiles / p.tiles_per_cta;
   const int64_t ctas = (int64_t)p.ctas_per_bh * Z * H;
   if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
@@ -1087,7 +1091,7 @@ static int attention_f16_dispatch(const void *Q, const void *K, const void *V, v
   DeviceInfo di;
   if (int e = current_device(&di)) return e;
   const float scale_log2 = sm_scale * 1.44269504f;
-  bool tma_ok = (D == 64 || D == 128) && !option("attn_force_simt", 0) && aligned16(Q) && aligned16(K) &&
+  bool tma_ok = (D == 64 || D == 128) && !option(OPT_attn_force_simt, 0) && aligned16(Q) && aligned16(K) &&
                 aligned16(V);
   for (int i = 0; i < 9 && tma_ok; ++i) tma_ok = s[i] % 8 == 0 && s[i] > 0;
   if (tma_ok) {

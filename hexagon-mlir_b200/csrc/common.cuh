@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/hexb.h"
 
 namespace hexb {
@@ -14,8 +16,39 @@ constexpr int kNumSMsB200 = 148;
 void set_cuda_error(cudaError_t e, const char *where);
 int check_launch(const char *where);  // cudaGetLastError -> status
 
-// Option store behind hexb_set_option / hexb_get_option.
-int option(const char *key, int dflt);
+// Option store behind hexb_set_option / hexb_get_option: one atomic word per option, indexed by an
+// enum, so that a launch reads its switches without a lock, a string or an allocation.
+// X(name): selectable kernel variants of the shipped library.
+#define HEXB_OPTIONS(X)                                                                              \
+  X(softmax_vpt_max) X(softmax_force_stream) X(softmax_ring) X(softmax_bulk_store) X(norm_ring)      \
+  X(norm_bulk_store) X(ring_bytes_per_warp) X(ring_map) X(norm_vpt_max) X(norm_force_stream)         \
+  X(norm_ctas_per_sm) X(norm_affine_f32) X(gemm_bn) X(gemm_tail_split) X(gemm_pair) X(gemm_epi_warps) \
+  X(gemm_tma_store) X(gemm_force_simt) X(attn_force_simt) X(attn_tiles_per_cta) X(attn_kernel)       \
+  X(attn_mask_tma) X(scan_force_scalar) X(scan_segments) X(scan_kv) X(decoder_fused_swiglu)          \
+  X(host_chunks) X(pdl) X(tmap_cache) X(wait_limit_us)
+// Descriptor-field overrides that can mis-describe an operand: compiled in only
+// with -DHEXB_DEV, absent from the shipped library's option table.
+#define HEXB_DEV_OPTIONS(X) X(gemm_b_lbo) X(gemm_b_sbo) X(attn_v_lbo) X(attn_v_sbo)
+enum Opt : int {
+#define HEXB_X(n) OPT_##n,
+  HEXB_OPTIONS(HEXB_X) HEXB_DEV_OPTIONS(HEXB_X)
+#undef HEXB_X
+      OPT_COUNT
+};
+int option(Opt key, int dflt);  // the value set through hexb_set_option, else dflt
+#ifdef HEXB_DEV
+#define HEXB_DEV_OPTION(key, dflt) ::hexb::option(key, dflt)
+#else
+#define HEXB_DEV_OPTION(key, dflt) (dflt)
+#endif
+
+// One-time set-up per device ordinal (function attributes).  The set-up calls are idempotent, so two
+// threads that both find the flag clear may both run them; the flag itself is never torn.
+struct PerDeviceOnce {
+  std::atomic<bool> done[64];
+  bool is_done(int dev) const { return done[dev & 63].load(std::memory_order_acquire); }
+  void mark(int dev) { done[dev & 63].store(true, std::memory_order_release); }
+};
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -66,7 +99,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = option("pdl", 1) ? 1 : 0;
+  cfg.numAttrs = option(OPT_pdl, 1) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -87,7 +87,7 @@ extern "C" int hexb_decoder_forward_f16(const hexb_decoder_config *cfg, const he
       return s;
     if ((s = hexb_matmul_f16(attn, w->wo[l], h, xin, T, d, d, d, d, d, HEXB_DT_F16, stream))) return s;
     if ((s = hexb_rms_norm_f16(h, n, w->g2[l], T, d, d, d, cfg->rms_eps, stream))) return s;
-    if (option("decoder_fused_swiglu", 1)) {
+    if (option(OPT_decoder_fused_swiglu, 1)) {
       if ((s = hexb_matmul_swiglu_f16(n, w->wgu[l], act, T, f, d, d, 2 * f, f, stream))) return s;
     } else {
       if ((s = hexb_matmul_f16(n, w->wgu[l], gu, nullptr, T, 2 * f, d, d, 2 * f, 2 * f, HEXB_DT_F16, stream))) return s;

@@ -34,7 +34,7 @@ constexpr int MAX_THREADS = 320;  // ... or eight epilogue warps: two per TMEM l
 // 8192 x 2304 x 768 808 -> 1034 TFLOP/s, with GELU 562 -> 766, 8192 x 768 x 3072 900 -> 971); long-K
 // products with many tiles run 1-2 % faster with four.
 static inline int launch_threads(int64_t M, int64_t N, int64_t K, int act, int sm_count) {
-  const int64_t forced = option("gemm_epi_warps", 0);
+  const int64_t forced = option(OPT_gemm_epi_warps, 0);
   if (forced) return forced == 8 ? MAX_THREADS : THREADS;
   const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
   return (act != 0 || K <= 1536 || tiles <= sm_count) ? MAX_THREADS : THREADS;
@@ -726,7 +726,7 @@ static StoreMap make_store_map(OutT *C, const __half *R, int64_t M, int64_t N, i
   sm.tm = fallback;
   sm.use = 0;
   sm.r_vec = R && aligned16(R) && ldr % 8 == 0;
-  if (!option("gemm_tma_store", 1) || !aligned16(C) || (ldc * (int64_t)sizeof(OutT)) % 16) return sm;
+  if (!option(OPT_gemm_tma_store, 1) || !aligned16(C) || (ldc * (int64_t)sizeof(OutT)) % 16) return sm;
   const uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
   int rc;
   if (sizeof(OutT) == 2) {
@@ -745,13 +745,13 @@ static StoreMap make_store_map(OutT *C, const __half *R, int64_t M, int64_t N, i
 template <typename OutT, int EPI, bool BT = false>
 static int launch_tc_pair(const EpiArgs &epi, const StoreMap &sm, const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M, int N,
                           int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count, cudaStream_t st) {
-  static bool attr_done[64] = {};
+  static PerDeviceOnce attr_done;
   int dev = 0;
   cudaGetDevice(&dev);
   auto kern = gemm_tc_pair_kernel<OutT, EPI, BT>;
-  if (!attr_done[dev & 63]) {
+  if (!attr_done.is_done(dev)) {
     HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES));
-    attr_done[dev & 63] = true;
+    attr_done.mark(dev);
   }
   constexpr int OUT_COLS = EPI == 1 ? pair::BN / 2 : pair::BN;
   const int tiles_m = (M + 255) / 256, tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
@@ -759,7 +759,7 @@ static int launch_tc_pair(const EpiArgs &epi, const StoreMap &sm, const CUtensor
   const int max_clusters = sm_count / 2;
   // the tiles of the last partial wave are cut in two column slices when both halves still fit one wave
   int full_items = tiles, split = 1;
-  if (EPI != 1 && tiles > max_clusters && option("gemm_tail_split", 1)) {
+  if (EPI != 1 && tiles > max_clusters && option(OPT_gemm_tail_split, 1)) {
     const int rem = tiles % max_clusters;
     if (rem > 0 && 2 * rem <= max_clusters) {
       full_items = tiles - rem;
@@ -779,13 +779,13 @@ static int launch_tc(const EpiArgs &epi, const StoreMap &sm, const CUtensorMap &
                      int N, int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count,
                      cudaStream_t st) {
   using cfg = Cfg<BN, STAGES>;
-  static bool attr_done[64] = {};
+  static PerDeviceOnce attr_done;
   int dev = 0;
   cudaGetDevice(&dev);
   auto kern = gemm_tc_kernel<BN, STAGES, OutT, EPI, BT>;
-  if (!attr_done[dev & 63]) {
+  if (!attr_done.is_done(dev)) {
     HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
-    attr_done[dev & 63] = true;
+    attr_done.mark(dev);
   }
   constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;  // output columns per tile
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + OUT_COLS - 1) / OUT_COLS;
@@ -793,14 +793,14 @@ static int launch_tc(const EpiArgs &epi, const StoreMap &sm, const CUtensorMap &
   // split the tiles of the last partial wave into column slices (>= 64 wide) while they still fit one wave
   int full_items = tiles / sm_count * sm_count, split = 1;
   const int rem = tiles - full_items;
-  if (EPI == 0 && !BT && rem > 0 && option("gemm_tail_split", 1)) {
+  if (EPI == 0 && !BT && rem > 0 && option(OPT_gemm_tail_split, 1)) {
     while (split * 2 <= BN / 64 && rem * split * 2 <= sm_count) split *= 2;
   }
   if (split == 1) full_items = tiles;
   const int items = full_items + (tiles - full_items) * split;
   const int grid = items < sm_count ? items : sm_count;
-  const uint32_t lbo = (uint32_t)option("gemm_b_lbo", BK * 128);
-  const uint32_t sbo = (uint32_t)option("gemm_b_sbo", 1024);
+  const uint32_t lbo = (uint32_t)HEXB_DEV_OPTION(OPT_gemm_b_lbo, BK * 128);
+  const uint32_t sbo = (uint32_t)HEXB_DEV_OPTION(OPT_gemm_b_sbo, 1024);
   launch_pdl(kern, dim3(grid), dim3(launch_threads(M, N, K, EPI == 1 ? 1 : epi.act, sm_count)), (size_t)cfg::SMEM_BYTES, st,
              tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok, lbo, sbo, full_items, split, epi, sm.tm, sm.use,
              sm.r_vec);
@@ -817,7 +817,7 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
   const int64_t ldr = ldc;
   const bool tc_ok = K > 0 && lda % 8 == 0 && ldb % 8 == 0 && aligned16(A) && aligned16(B) &&
                      M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31) &&
-                     !option("gemm_force_simt", 0);
+                     !option(OPT_gemm_force_simt, 0);
   if (!tc_ok) {
     dim3 grid((unsigned)((N + 15) / 16), (unsigned)((M + 15) / 16));
     if (grid.y > 65535) return HEXB_ERR_UNSUPPORTED;
@@ -846,7 +846,7 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
   const int vec_ok = (ldc % EV == 0) && aligned16(C) && (!R || (sizeof(OutT) == 2 && aligned16(R)));
   const StoreMap sm = make_store_map<OutT>(C, R, M, N, ldc, ldr, tmA);
   const int tiles_m = (int)((M + BM - 1) / BM);
-  int bn = option("gemm_bn", 0);
+  int bn = option(OPT_gemm_bn, 0);
   if (bn != 64 && bn != 128 && bn != 256) {
     bn = 256;
     if (N <= 64 || (int64_t)tiles_m * ((N + 127) / 128) < di.sm_count / 2) bn = 64;
@@ -854,7 +854,7 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
   }
   // CTA-pair kernel for problems with at least one 256 x 256 tile per pair of SMs
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
-  if (option("gemm_bn", 0) == 0 && option("gemm_pair", 1) && pair_tiles >= di.sm_count / 2)
+  if (option(OPT_gemm_bn, 0) == 0 && option(OPT_gemm_pair, 1) && pair_tiles >= di.sm_count / 2)
     return launch_tc_pair<OutT, EPI, BT>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
   if (BT && bn == 64) bn = 128;  // the transposed form loads Bt in 128-row boxes
   switch (bn) {
@@ -967,7 +967,7 @@ extern "C" int hexb_matmul_swiglu_f16(const void *A, const void *B_gate_up, void
   }
   const int vec_ok = (ldo % 8 == 0) && aligned16(out);
   const gemm::StoreMap sm = gemm::make_store_map<__half>((__half *)out, nullptr, M, F, ldo, ldo, tmA);
-  if (option("gemm_pair", 1) && ((M + 255) / 256) * ((F + 127) / 128) >= di.sm_count / 2)
+  if (option(OPT_gemm_pair, 1) && ((M + 255) / 256) * ((F + 127) / 128) >= di.sm_count / 2)
     return launch_tc_pair<__half, 1>(gemm::EpiArgs{nullptr, 0}, sm, tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
                                      di.sm_count, (cudaStream_t)stream);
   return launch_tc<256, 4, __half, 1>(gemm::EpiArgs{nullptr, 0}, sm, tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,

@@ -143,6 +143,31 @@ __device__ __forceinline__ uint32_t h2_norm_scale(uint32_t w, float rstd, uint32
       : "=r"(out) : "r"(w), "f"(rstd), "r"(g));
   return out;
 }
+// The same two steps with the affine part in fp32 and ONE rounding at the end, as the reference's
+// fp32 expression (x - mean) * rstd * w + b rounds (test/python/triton/test_layer_norm.py:78-81).
+__device__ __forceinline__ uint32_t h2_norm_affine_f32(uint32_t w, float mean, float rstd, uint32_t g, uint32_t b) {
+  uint32_t out;
+  asm("{\n\t.reg .b16 lo, hi, glo, ghi, blo, bhi;\n\t.reg .f32 d0, d1, g0, g1, b0, b1;\n\t"
+      "mov.b32 {lo, hi}, %1;\n\tmov.b32 {glo, ghi}, %4;\n\tmov.b32 {blo, bhi}, %5;\n\t"
+      "sub.rn.f32.f16 d0, lo, %2;\n\tsub.rn.f32.f16 d1, hi, %2;\n\t"
+      "mul.rn.f32 d0, d0, %3;\n\tmul.rn.f32 d1, d1, %3;\n\t"
+      "cvt.f32.f16 g0, glo;\n\tcvt.f32.f16 g1, ghi;\n\tcvt.f32.f16 b0, blo;\n\tcvt.f32.f16 b1, bhi;\n\t"
+      "fma.rn.f32 d0, d0, g0, b0;\n\tfma.rn.f32 d1, d1, g1, b1;\n\t"
+      "cvt.rn.f16x2.f32 %0, d1, d0;\n\t}"
+      : "=r"(out) : "r"(w), "f"(mean), "f"(rstd), "r"(g), "r"(b));
+  return out;
+}
+__device__ __forceinline__ uint32_t h2_norm_scale_f32(uint32_t w, float rstd, uint32_t g) {
+  uint32_t out;
+  asm("{\n\t.reg .b16 lo, hi, glo, ghi;\n\t.reg .f32 d0, d1, g0, g1;\n\t"
+      "mov.b32 {lo, hi}, %1;\n\tmov.b32 {glo, ghi}, %3;\n\t"
+      "cvt.f32.f16 d0, lo;\n\tcvt.f32.f16 d1, hi;\n\tcvt.f32.f16 g0, glo;\n\tcvt.f32.f16 g1, ghi;\n\t"
+      "mul.rn.f32 d0, d0, %2;\n\tmul.rn.f32 d1, d1, %2;\n\t"
+      "mul.rn.f32 d0, d0, g0;\n\tmul.rn.f32 d1, d1, g1;\n\t"
+      "cvt.rn.f16x2.f32 %0, d1, d0;\n\t}"
+      : "=r"(out) : "r"(w), "f"(rstd), "r"(g));
+  return out;
+}
 __device__ __forceinline__ uint32_t &word(uint4 &v, int c) { return c == 0 ? v.x : c == 1 ? v.y : c == 2 ? v.z : v.w; }
 
 static __device__ int g_norm_status = 0;
@@ -155,17 +180,16 @@ __global__ void __launch_bounds__(ring::THREADS, 1)
 norm_ring_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict__ w,
                  const T *__restrict__ b, float *__restrict__ mean_out, float *__restrict__ rstd_out,
                  int64_t rows, int nvec, int64_t xs, int64_t ys, float inv_n, float eps, int slots,
-                 int slot_bytes, int map, int dbg, int out_slots) {
+                 int slot_bytes, int map, int out_slots, int affine_f32) {
   constexpr int E = Vec16<T>::N;
   using Raw = decltype(Vec16<T>::raw);
   extern __shared__ uint8_t smem_raw[];
   // out_slots > 0: a finished row is written to a shared-memory slot and leaves as one bulk store
-  ring::WarpRing rg = ring::setup(smem_raw, slots, slot_bytes, (dbg >> 8) & 1, out_slots);
+  ring::WarpRing rg = ring::setup(smem_raw, slots, slot_bytes, 0, out_slots);
   int n_out = 0;
   pdl_launch_dependents();
   pdl_wait();  // the ring is set up; from here on global memory is touched
-  const int store_mode = (dbg >> 4) & 3;
-  dbg &= 15;
+  constexpr int store_mode = 0;  // streaming stores (default-policy, .cs and evict-first hints measured within noise)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t row_bytes = (uint32_t)nvec * 16u;
   const ring::RowWalk walk = ring::row_walk(rows, map);
@@ -277,16 +301,6 @@ norm_ring_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict
       }
     }
     T *yr = y + r * ys;
-    if (dbg) {  // measurement aid: 1 = no output stores, 2 = store the row unchanged
-      if (dbg == 2) {
-#pragma unroll
-        for (int j = 0; j < VPL; ++j)
-          if (lane + 32 * j < nvec)
-            ring::store_out16(yr + (int64_t)(lane + 32 * j) * E, *reinterpret_cast<uint4 *>(&xv[j].raw), store_mode, rg.policy);
-      }
-      if (++s == slots) { s = 0; phase ^= 1u; }
-      continue;
-    }
     uint32_t oslot = 0;
     if (out_slots) {
       // the bulk store that last used this output slot has finished reading it
@@ -307,14 +321,17 @@ norm_ring_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict
           uint4 o;
           if constexpr (RMS) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) word(o, c) = h2_norm_scale(word(xr, c), rstd, word(gr, c));
+            for (int c = 0; c < 4; ++c)
+              word(o, c) = affine_f32 ? h2_norm_scale_f32(word(xr, c), rstd, word(gr, c))
+                                      : h2_norm_scale(word(xr, c), rstd, word(gr, c));
           } else {
             uint4 br;
             if constexpr (B_SMEM) br = ring::lds128(rg.extra + (uint32_t)vi * 16u);
             else br = *reinterpret_cast<uint4 *>(&bv[j].raw);
 #pragma unroll
             for (int c = 0; c < 4; ++c)
-              word(o, c) = h2_norm_affine(word(xr, c), mean, rstd, word(gr, c), word(br, c));
+              word(o, c) = affine_f32 ? h2_norm_affine_f32(word(xr, c), mean, rstd, word(gr, c), word(br, c))
+                                      : h2_norm_affine(word(xr, c), mean, rstd, word(gr, c), word(br, c));
           }
           if (out_slots) ring::sts128(oslot + (uint32_t)vi * 16u, o);
           else ring::store_out16(yr + (int64_t)vi * E, o, store_mode, rg.policy);
@@ -363,20 +380,21 @@ static int launch_norm_ring(const T *x, T *y, const T *w, const T *b, float *mea
                             int64_t rows, int nvec, int64_t xs, int64_t ys, float inv_n, float eps,
                             int sm_count, cudaStream_t st) {
   // rows leave as one bulk store each from a per-warp output slot (measured 44.3 -> 43.7 us on [16384 x 4096] fp16)
-  const int out_slots = option("norm_bulk_store", 1) ? 1 : 0;
+  const int out_slots = option(OPT_norm_bulk_store, 1) ? 1 : 0;
   const ring::Layout lay = ring::make_layout(nvec * 16, 0, out_slots);
   auto kern = norm_ring_kernel<T, VPL, RMS>;
-  static bool attr_done[64] = {};
+  static PerDeviceOnce attr_done;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_done[dev & 63]) {
+  if (!attr_done.is_done(dev)) {
     HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 212 * 1024));
-    attr_done[dev & 63] = true;
+    attr_done.mark(dev);
   }
   const int64_t groups = (rows + ring::WARPS - 1) / ring::WARPS;
   const int grid = (int)(groups < sm_count ? groups : sm_count);
   launch_pdl(kern, dim3(grid), dim3(ring::THREADS), (size_t)lay.smem_bytes, st, x, y, w, b, mean, rstd, rows, nvec, xs, ys,
-             inv_n, eps, lay.slots, lay.slot_bytes, (int)option("ring_map", 0), (int)option("ring_dbg", 0), out_slots);
+             inv_n, eps, lay.slots, lay.slot_bytes, (int)option(OPT_ring_map, 0), out_slots,
+             (int)option(OPT_norm_affine_f32, 1));
   return check_launch(RMS ? "rms_norm_ring" : "layer_norm_ring");
 }
 
@@ -441,7 +459,7 @@ static int norm_launch(const T *x, T *y, const T *w, const T *b, float *mean, fl
   const bool vec_ok = (cols % E == 0) && (xs % E == 0) && (ys % E == 0) && aligned16(x) &&
                       aligned16(y) && aligned16(w) && (RMS || aligned16(b));
   const int64_t row_bytes = cols * (int64_t)sizeof(T);
-  if (vec_ok && option("norm_ring", 1) && row_bytes >= 512 && row_bytes <= ring::MAX_ROW_BYTES &&
+  if (vec_ok && option(OPT_norm_ring, 1) && row_bytes >= 512 && row_bytes <= ring::MAX_ROW_BYTES &&
       rows * row_bytes >= (4ll << 20)) {
     const int nvec = (int)(cols / E);
     const int need = (nvec + 31) / 32;
@@ -456,10 +474,10 @@ static int norm_launch(const T *x, T *y, const T *w, const T *b, float *mean, fl
 #undef RING
   }
   int tpr = 0, vpt = 0;
-  const int vpt_max = option("norm_vpt_max", sizeof(T) == 2 ? 4 : 8);
-  if (vec_ok && !option("norm_force_stream", 0) && choose_row_shape(cols / E, vpt_max, &tpr, &vpt)) {
+  const int vpt_max = option(OPT_norm_vpt_max, sizeof(T) == 2 ? 4 : 8);
+  if (vec_ok && !option(OPT_norm_force_stream, 0) && choose_row_shape(cols / E, vpt_max, &tpr, &vpt)) {
     const int nvec = (int)(cols / E);
-    const int waves = option("norm_ctas_per_sm", 8);
+    const int waves = option(OPT_norm_ctas_per_sm, 8);
 #define LAUNCH(TPR, VPT)                                                                          \
   {                                                                                               \
     constexpr int TH = CtaThreads<TPR>::value;                                                    \

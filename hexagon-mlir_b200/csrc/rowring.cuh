@@ -80,7 +80,7 @@ struct Layout {
 inline Layout make_layout(int row_bytes, int extra_bytes = 0, int out_slots = 0) {
   Layout l;
   l.slot_bytes = (row_bytes + 127) / 128 * 128;
-  l.slots = option("ring_bytes_per_warp", RING_BYTES_PER_WARP) / l.slot_bytes;
+  l.slots = option(OPT_ring_bytes_per_warp, RING_BYTES_PER_WARP) / l.slot_bytes;
   if (l.slots < 1) l.slots = 1;
   if (l.slots > MAX_SLOTS) l.slots = MAX_SLOTS;
   // [ring buffers][barriers][abort flag, pad to 128][extra][slack for the 128-byte alignment]

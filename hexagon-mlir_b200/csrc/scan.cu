@@ -245,7 +245,7 @@ static int launch_rows(const T *x, T *y, int64_t outer, int64_t len, int reverse
     if (segs > max_segs) segs = max_segs;
     if (segs < 1) segs = 1;
   }
-  if (int64_t forced = option("scan_segments", 0)) segs = forced;
+  if (int64_t forced = option(OPT_scan_segments, 0)) segs = forced;
   int64_t seg_len = (len + segs - 1) / segs;
   seg_len = (seg_len + chunk - 1) / chunk * chunk;  // whole chunks: vector accesses stay aligned
   segs = (len + seg_len - 1) / seg_len;
@@ -274,7 +274,7 @@ static int run(const T *x, T *y, int64_t outer, int64_t len, int64_t inner, int 
   if (inner > 1) {
     const int64_t cols = outer * inner;
     constexpr int EV = 16 / (int)sizeof(T);
-    const bool vecs = inner % EV == 0 && aligned16(x) && aligned16(y) && !option("scan_force_scalar", 0);
+    const bool vecs = inner % EV == 0 && aligned16(x) && aligned16(y) && !option(OPT_scan_force_scalar, 0);
     const int64_t groups = vecs ? cols / EV : cols;            // threads along the columns
     const int64_t grp_ctas = (groups + THREADS - 1) / THREADS;
     const int64_t col_ctas = (cols + THREADS - 1) / THREADS;
@@ -288,7 +288,7 @@ static int run(const T *x, T *y, int64_t outer, int64_t len, int64_t inner, int 
     const int64_t by_scratch = ((int64_t)16 << 20) / (cols * 2 * (int64_t)sizeof(A));
     if (segs > by_scratch) segs = by_scratch;
     if (segs < 1) segs = 1;
-    if (int64_t forced = option("scan_segments", 0)) segs = forced < 65535 ? forced : 65535;
+    if (int64_t forced = option(OPT_scan_segments, 0)) segs = forced < 65535 ? forced : 65535;
     const int64_t seg_len = (len + segs - 1) / segs;
     segs = (len + seg_len - 1) / seg_len;
     const dim3 grid((unsigned)grp_ctas, (unsigned)segs);
@@ -308,9 +308,9 @@ static int run(const T *x, T *y, int64_t outer, int64_t len, int64_t inner, int 
   }
   constexpr int E = 16 / (int)sizeof(T);
   const bool vec = !reverse && aligned16(x) && aligned16(y) && (outer == 1 || len % E == 0) &&
-                   !option("scan_force_scalar", 0);
+                   !option(OPT_scan_force_scalar, 0);
   const int64_t per_kv = (int64_t)WARPS * 32 * (vec ? E : 1);   // elements of a chunk per unit of KV
-  const int64_t kv_cap = option("scan_kv", 2);
+  const int64_t kv_cap = option(OPT_scan_kv, 2);
   if (vec) {
     if (len >= 4 * per_kv && kv_cap >= 4) return launch_rows<T, true, 4>(x, y, outer, len, reverse, di.sm_count, st);
     if (len >= 2 * per_kv && kv_cap >= 2) return launch_rows<T, true, 2>(x, y, outer, len, reverse, di.sm_count, st);

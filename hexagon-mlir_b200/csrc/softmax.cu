@@ -80,7 +80,7 @@ static __device__ int g_softmax_status = 0;
 template <typename T, int VPL>
 __global__ void __launch_bounds__(ring::THREADS, 1)
 softmax_ring_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, int nvec, int64_t xs,
-                    int64_t ys, int slots, int slot_bytes, int map, int dbg, int out_slots) {
+                    int64_t ys, int slots, int slot_bytes, int map, int out_slots) {
   constexpr int E = Vec16<T>::N;
   using Raw = decltype(Vec16<T>::raw);
   extern __shared__ uint8_t smem_raw[];
@@ -184,20 +184,20 @@ softmax_ring_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows, in
 template <typename T, int VPL>
 static int launch_softmax_ring(const T *x, T *y, int64_t rows, int nvec, int64_t xs, int64_t ys,
                                int sm_count, cudaStream_t st) {
-  const int out_slots = (int)option("softmax_bulk_store", 0);  // measured slower here ([8192 x 1024] fp32: 12.6 vs 12.4 us)
+  const int out_slots = (int)option(OPT_softmax_bulk_store, 0);  // measured slower here ([8192 x 1024] fp32: 12.6 vs 12.4 us)
   const ring::Layout lay = ring::make_layout(nvec * 16, 0, out_slots);
   auto kern = softmax_ring_kernel<T, VPL>;
-  static bool attr_done[64] = {};
+  static PerDeviceOnce attr_done;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_done[dev & 63]) {
+  if (!attr_done.is_done(dev)) {
     HEXB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr_done[dev & 63] = true;
+    attr_done.mark(dev);
   }
   const int64_t groups = (rows + ring::WARPS - 1) / ring::WARPS;
   const int grid = (int)(groups < sm_count ? groups : sm_count);
   launch_pdl(kern, dim3(grid), dim3(ring::THREADS), (size_t)lay.smem_bytes, st, x, y, rows, nvec, xs, ys, lay.slots,
-             lay.slot_bytes, (int)option("ring_map", 0), (int)option("ring_dbg", 0), out_slots);
+             lay.slot_bytes, (int)option(OPT_ring_map, 0), out_slots);
   return check_launch("softmax_ring");
 }
 
@@ -259,7 +259,7 @@ static int softmax_launch(const T *x, T *y, int64_t rows, int64_t cols, int64_t 
   const int64_t row_bytes = cols * (int64_t)sizeof(T);
   // The ring form is kept selectable; for the row sizes measured (4 KiB rows) the register kernel
   // below is faster (11.8 vs 12.6 us on [8192 x 1024] fp32), so it is off by default.
-  if (vec_ok && option("softmax_ring", 0) && row_bytes >= 512 && row_bytes <= ring::MAX_ROW_BYTES &&
+  if (vec_ok && option(OPT_softmax_ring, 0) && row_bytes >= 512 && row_bytes <= ring::MAX_ROW_BYTES &&
       rows * row_bytes >= (4ll << 20)) {
     const int nvec = (int)(cols / E);
     const int need = (nvec + 31) / 32;
@@ -272,8 +272,8 @@ static int softmax_launch(const T *x, T *y, int64_t rows, int64_t cols, int64_t 
 #undef RING
   }
   int tpr = 0, vpt = 0;
-  if (vec_ok && !option("softmax_force_stream", 0) &&
-      choose_row_shape(cols / E, option("softmax_vpt_max", 8), &tpr, &vpt)) {
+  if (vec_ok && !option(OPT_softmax_force_stream, 0) &&
+      choose_row_shape(cols / E, option(OPT_softmax_vpt_max, 8), &tpr, &vpt)) {
     const int nvec = (int)(cols / E);
 #define LAUNCH(TPR, VPT)                                                                       \
   {                                                                                            \

@@ -55,11 +55,14 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 
 // Bounded wait.  Spins on try_wait; every 512 polls it looks at the CTA's abort flag and at the
-// wall clock.  After kWaitLimitNs without progress it raises the abort flag, so that every other
+// wall clock.  After limit_ns without progress it raises the abort flag, so that every other
 // role of the CTA leaves its own wait too, and returns false.  Callers fall through to the common
 // teardown (no trap, no endless loop); the host sees HEXB_ERR_TIMEOUT in the status word.
+// The kernels of the library wait with the 2 s default; the self-test kernel behind
+// hexb_selftest_bounded_wait passes a short limit so that a test can watch a wait run out.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
@@ -68,7 +71,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
+      else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         return false;
       }

@@ -79,6 +79,59 @@ int encode_tmap_f32_sw128_2d(CUtensorMap *out, const void *base, const uint64_t 
   return HEXB_OK;
 }
 
+// ------------------------------------------------------------------ bounded-wait self-test
+// One CTA with the role layout of the tensor-core kernels (warp 0 producer, warp 1 owner of the TMEM
+// allocation, warps 2-5 consumers).  It initialises one mbarrier that nothing ever arrives on; the
+// producer waits on it with the given limit, gives up, raises the CTA's abort flag; the consumers,
+// waiting on the same barrier with the default limit, see the flag at their next look and leave too;
+// everyone meets at the common teardown, the TMEM columns are released and the status word is set.
+static __device__ int g_selftest_status = 0;
+
+__global__ void __launch_bounds__(192, 1) bounded_wait_selftest_kernel(unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_word;
+  volatile int *abort_flag = &abort_word;
+  const uint32_t bar = tc::smem_u32(&bar_storage);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(bar, 1);
+    abort_word = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tc::smem_u32(&tmem_slot), 32);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  bool ok = true;
+  if (warp == 0) {
+    if (lane == 0) ok = tc::mbar_wait(bar, 0, abort_flag, limit_ns);   // runs out: nobody arrives
+  } else if (warp >= 2) {
+    ok = tc::mbar_wait(bar, 0, abort_flag);                            // leaves through the abort flag
+  }
+  (void)ok;
+  // common teardown, as in the tensor-core kernels
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, 32);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_selftest_status, (int)HEXB_ERR_TIMEOUT);
+}
+
+static int selftest_device_status_fetch_and_clear(int *out) {
+  int v = 0, zero = 0;
+  HEXB_CUDA_OK(cudaMemcpyFromSymbol(&v, g_selftest_status, sizeof(int)));
+  if (v) HEXB_CUDA_OK(cudaMemcpyToSymbol(g_selftest_status, &zero, sizeof(int)));
+  *out = v;
+  return HEXB_OK;
+}
+
 int gemm_device_status_fetch_and_clear(int *out);
 int attn_device_status_fetch_and_clear(int *out);
 int norm_device_status_fetch_and_clear(int *out);
@@ -91,12 +144,22 @@ extern "C" int hexb_device_status(int *out) {
   using namespace hexb;
   if (!out) return HEXB_ERR_BAD_ARG;
   HEXB_CUDA_OK(cudaDeviceSynchronize());
-  int v[5] = {0, 0, 0, 0, 0};
+  int v[6] = {0, 0, 0, 0, 0, 0};
   if (int s = gemm_device_status_fetch_and_clear(&v[0])) return s;
   if (int s = attn_device_status_fetch_and_clear(&v[1])) return s;
   if (int s = norm_device_status_fetch_and_clear(&v[2])) return s;
   if (int s = softmax_device_status_fetch_and_clear(&v[3])) return s;
   if (int s = embed_device_status_fetch_and_clear(&v[4])) return s;
-  *out = v[0] ? v[0] : v[1] ? v[1] : v[2] ? v[2] : v[3] ? v[3] : v[4];
+  if (int s = selftest_device_status_fetch_and_clear(&v[5])) return s;
+  *out = v[0] ? v[0] : v[1] ? v[1] : v[2] ? v[2] : v[3] ? v[3] : v[4] ? v[4] : v[5];
   return HEXB_OK;
+}
+
+extern "C" int hexb_selftest_bounded_wait(int limit_us, void *stream) {
+  using namespace hexb;
+  if (limit_us < 1 || limit_us > 1000000) return HEXB_ERR_BAD_ARG;   // 1 us .. 1 s
+  DeviceInfo di;
+  if (int e = current_device(&di)) return e;
+  bounded_wait_selftest_kernel<<<1, 192, 0, (cudaStream_t)stream>>>((unsigned long long)limit_us * 1000ull);
+  return check_launch("bounded_wait_selftest");
 }

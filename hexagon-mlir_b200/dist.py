@@ -70,7 +70,7 @@ PARTITIONS = {
 }
 
 
-def _units_view(name: str, t: torch.Tensor) -> torch.Tensor:
+def units_view(name: str, t: torch.Tensor) -> torch.Tensor:
     """The tensor with its partition units along dimension 0."""
     if name == "attention":
         if t.dim() != 4:
@@ -88,13 +88,13 @@ def partition(name: str, inputs: dict, world_size: int, rank: int) -> dict:
         raise KeyError(f"{name}: missing operands {missing}")
     out = {k: inputs[k] for k in whole}
     for k in cut:
-        out[k] = shard_rows(_units_view(name, inputs[k]), world_size, rank)
+        out[k] = shard_rows(units_view(name, inputs[k]), world_size, rank)
     return out
 
 
 def units_of(name: str, inputs: dict) -> int:
     """Number of independent units (rows, (batch, head) pairs, sequences) in the whole problem."""
-    return _units_view(name, inputs[PARTITIONS[name][1][0]]).shape[0]
+    return units_view(name, inputs[PARTITIONS[name][1][0]]).shape[0]
 
 
 def run_partitioned(name: str, inputs: dict, compute, world_size: int, rank: int, group=None, gather: bool = True):

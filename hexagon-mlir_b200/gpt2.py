@@ -106,7 +106,7 @@ class GPT2Runner:
         return self._bufs[key]
 
     def forward(self, input_ids: torch.Tensor, logits_dtype=torch.float32, graph: bool = False,
-                last_only: bool = False) -> torch.Tensor:
+                last_only: bool = False, check_ids: bool = False) -> torch.Tensor:
         """input_ids: int64 [batch, seq] on the runner's device.  Returns logits [batch, seq, vocab]
         (a buffer owned by the runner, overwritten by the next call with the same shape).
 
@@ -115,13 +115,22 @@ class GPT2Runner:
         top-5 comparison -- reads; the LM head is more than half of a full forward pass.
 
         graph=True replays the 17 launches as one CUDA graph captured on the first call with this
-        (batch, seq, logits dtype): for short prompts the launches, not the kernels, set the latency."""
+        (batch, seq, logits dtype): for short prompts the launches, not the kernels, set the latency.
+
+        check_ids=True validates the token ids against the vocabulary before the launches (one device
+        synchronisation) and raises IndexError for a bad one, as the torch model does.  Without it an
+        out-of-range id embeds as a zero row and only the device status word records it: callers that
+        replay graphs should poll hexb200.device_status() between requests."""
         cfg = self.cfg
         if input_ids.dim() != 2 or input_ids.dtype != torch.int64 or input_ids.device != self.device:
             raise ValueError("GPT2Runner: int64 [batch, seq] ids on the runner's device expected")
         B, S = input_ids.shape
         if S > cfg.n_positions:
             raise ValueError("GPT2Runner: sequence longer than n_positions")
+        if check_ids and input_ids.numel():
+            lo, hi = int(input_ids.min()), int(input_ids.max())
+            if lo < 0 or hi >= cfg.vocab_size:
+                raise IndexError(f"GPT2Runner: token id {lo if lo < 0 else hi} is outside [0, {cfg.vocab_size})")
         if not graph:
             return self._forward(input_ids.contiguous(), logits_dtype, last_only)
         key = (B, S, logits_dtype, last_only)

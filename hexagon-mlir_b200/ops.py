@@ -14,7 +14,7 @@ import math
 import torch
 
 from . import _lib
-from ._lib import HEXB_DT_F16, HEXB_DT_F32, check
+from ._lib import HEXB_DT_F16, HEXB_DT_F32, HEXB_DT_I32, check
 
 _DT = {torch.float16: HEXB_DT_F16, torch.float32: HEXB_DT_F32}
 
@@ -215,9 +215,18 @@ def linear(a, w, c, bias=None, residual=None, act: str = "none", w_transposed: b
                                   int(bool(w_transposed)), acts[act], _dt(c), _stream(a)), "linear")
 
 
-def embedding(wte, wpe, ids, out) -> None:
-    """out[b, s, :] = wte[ids[b, s], :] + wpe[s, :] for float16 tables and int64 ids [batch, seq]."""
+def embedding(wte, wpe, ids, out, check_ids: bool = False) -> None:
+    """out[b, s, :] = wte[ids[b, s], :] + wpe[s, :] for float16 tables and int64 ids [batch, seq].
+
+    The kernel writes a zero row for an id outside [0, vocab) and records HEXB_ERR_BAD_ARG in the
+    device status word (read it with ``hexb200.device_status()``; a CUDA-graph replay has no other
+    way to report it).  ``check_ids=True`` validates the ids first -- one device synchronisation --
+    and raises IndexError as torch's own embedding lookup does."""
     lib = _lib.load()
+    if check_ids and ids.numel():
+        lo, hi = int(ids.min()), int(ids.max())
+        if lo < 0 or hi >= wte.shape[0]:
+            raise IndexError(f"embedding: token id {lo if lo < 0 else hi} is outside [0, {wte.shape[0]})")
     if any(t.device.type != "cuda" for t in (wte, wpe, ids, out)):
         return _stage(lambda wte, wpe, ids, out: embedding(wte, wpe, ids, out), dict(wte=wte, wpe=wpe, ids=ids, out=out),
                       ("out",))
@@ -481,7 +490,7 @@ def cumsum(x, out, axis: int = -1, reverse: bool = False) -> None:
     if x.dim() == 0:
         raise ValueError("cumsum: a scalar has no axis")
     axis = axis % x.dim()
-    dt = {torch.float16: HEXB_DT_F16, torch.float32: HEXB_DT_F32, torch.int32: 3}.get(x.dtype)
+    dt = {torch.float16: HEXB_DT_F16, torch.float32: HEXB_DT_F32, torch.int32: HEXB_DT_I32}.get(x.dtype)
     if dt is None:
         raise TypeError(f"cumsum: unsupported dtype {x.dtype}")
     outer = math.prod(x.shape[:axis])

@@ -40,8 +40,9 @@ enum {
   HEXB_ERR_NO_DEVICE = -7    /* no sm_100 device is current                                  */
 };
 
-/* dtype ids: the ids of the reference's raw tensor files (test/utils/dsp/include/tensor.h:26-38) */
-enum { HEXB_DT_F16 = 1, HEXB_DT_F32 = 2, HEXB_DT_I32 = 3 /* hexb_cumsum only */ };
+/* dtype ids: the ids of the reference's raw tensor files (test/utils/dsp/include/tensor.h:26-38:
+ * Float16 = 1, Float32 = 2, Int32 = 6; the other ids of that list name types no kernel here takes). */
+enum { HEXB_DT_F16 = 1, HEXB_DT_F32 = 2, HEXB_DT_I32 = 6 /* hexb_cumsum only */ };
 
 int hexb_version(void);
 const char *hexb_status_string(int status);
@@ -50,8 +51,16 @@ const char *hexb_last_cuda_error(void);
 /* Synchronises the current device, then reports and clears the sticky device-side status word
  * that bounded waits inside the tensor-core kernels set when they give up.  *out = HEXB_OK or
  * HEXB_ERR_TIMEOUT.  Replaces: DMAStatus out-param of the UserDMA runtime
- * (bin/runtime/UserDMA/RuntimeDMA.h:18). */
+ * (qcom_hexagon_backend/bin/runtime/include/RuntimeDMA.h:18). */
 int hexb_device_status(int *out);
+/* Self-test of that mechanism: launches one small CTA (producer / TMEM owner / consumer warps as in
+ * the tensor-core kernels) whose only mbarrier is never arrived on.  The producer's wait runs out
+ * after `limit_us` microseconds (1 .. 1 000 000), the other warps leave through the CTA's abort flag,
+ * the common teardown releases the tensor memory, and the next hexb_device_status() reports
+ * HEXB_ERR_TIMEOUT once.  The kernel returns by construction; nothing faults or traps.
+ * Replaces: the 100 ms acquire timeout of the runtime's resource manager
+ * (qcom_hexagon_backend/bin/runtime/src/HexagonAPI.cpp:57), the only bounded wait of the reference. */
+int hexb_selftest_bounded_wait(int limit_us, void *stream);
 
 /* ---- row softmax.  Replaces: softmax_kernel(x_ptr, output_ptr, NUM_ROWS, NUM_COLS, BLOCK_SIZE)
  * (test/python/triton/test_softmax.py:44-72) and online_softmax(...)
@@ -245,7 +254,11 @@ int hexb_decoder_forward_f16(const hexb_decoder_config *cfg, const hexb_decoder_
  *     d_ff 8192, or 10082 tokens at d_model 256 / d_ff 512).
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
  *     with that device current) and caches it; make that first call before starting any stream
- *     capture.
+ *     capture.  With the CUDA runtime's lazy module loading that first call is also the moment the
+ *     driver instantiates the library's image on the device -- the array itself, the kernels' code
+ *     and their function attributes -- so a host that hands the device's memory to its own pool must
+ *     make one call (a tiny configuration will do) BEFORE it claims the rest of the memory;
+ *     afterwards no call changes the amount of free device memory.
  *   - All calls on a device share the one array.  It keeps whatever the previous call left there;
  *     the block stack writes every intermediate before reading it, so nothing has to be cleared.
  *     Two calls that overlap on the GPU (different streams, or different host threads) race on
@@ -271,8 +284,10 @@ int hexb_attention_fwd_host(int dtype, const void *Q, const void *K, const void 
 /* Releases the cached staging memory of the current device. */
 int hexb_host_staging_release(void);
 
-/* ---- tuning knob for experiments: selects a kernel variant by name ("ln_variant", ...).
- * Unknown keys return HEXB_ERR_BAD_ARG.  Replaces: the per-launch HexagonOptions overrides
+/* ---- variant switches: selects a kernel variant by name ("attn_kernel", "gemm_pair", "norm_ring",
+ * "pdl", ...; the table is in INTEGRATION.md).  Every value of every key computes the same result by
+ * another route.  Unknown keys return HEXB_ERR_BAD_ARG; hexb_get_option returns HEXB_ERR_BAD_ARG for a
+ * key that was never set (the launchers then use their built-in defaults).  Replaces: the per-launch HexagonOptions overrides
  * (qcom_hexagon_backend/backend/hexagon_options.py:16-107). */
 int hexb_set_option(const char *key, int value);
 int hexb_get_option(const char *key, int *value);

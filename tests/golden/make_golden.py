@@ -13,7 +13,7 @@ The reference's test modules are imported unmodified with
 
 Each fixture ``<case>.npz`` holds the recorded inputs (in0, in1, ...), ``output`` (what the
 reference kernel produced) and ``expected`` (the torch value the reference test asserted against).
-Usage: ``python tests/golden/make_golden.py``.
+Usage: ``HEXAGON_MLIR_REF=<checkout of qualcomm/hexagon-mlir> python tests/golden/make_golden.py``.
 """
 import importlib
 import os
@@ -26,7 +26,9 @@ import numpy as np  # noqa: E402
 import torch  # noqa: E402
 import triton  # noqa: E402
 
-REF = Path(os.environ.get("HEXAGON_MLIR_REF", "/root/reference"))
+if not os.environ.get("HEXAGON_MLIR_REF"):
+    raise SystemExit("set HEXAGON_MLIR_REF to a checkout of qualcomm/hexagon-mlir")
+REF = Path(os.environ["HEXAGON_MLIR_REF"])
 OUT = Path(__file__).resolve().parent
 
 

@@ -56,6 +56,10 @@ def test_option_store():
     assert lib.hexb_set_option(b"not_an_option", 1) == -1
     assert lib.hexb_set_option(None, 1) == -1
     assert lib.hexb_get_option(b"never_set_gemm_bn_like", C.byref(v)) == -1
+    assert lib.hexb_get_option(b"gemm_bn", C.byref(v)) == -1          # a known key that was never set
+    # switches that could make a kernel skip work or mis-describe an operand are not in the shipped table
+    for dev_only in (b"ring_dbg", b"gemm_b_lbo", b"gemm_b_sbo", b"attn_v_lbo", b"attn_v_sbo"):
+        assert lib.hexb_set_option(dev_only, 1) == -1
     with pytest.raises(hexb200.HexbError):
         hexb200.set_option("nope", 1)
 

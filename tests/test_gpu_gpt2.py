@@ -116,6 +116,45 @@ def test_gpt2_two_layers_vs_oracle_and_transformers(B, S):
     assert O.max_rel_err(l16[:nb], ref) < REL_F16
 
 
+def test_gpt2_strict_top5_rule_with_separated_logits():
+    """The reference's acceptance rule as written (gpt2lmheadmodel.py:74-92: the same five tokens in the
+    same order, values within rtol 0.03), with no tie band: five embedding rows are given a component
+    along the final LayerNorm's bias, of decreasing size, so that their logits lead the other 50252 by
+    margins far above fp16 resolution whatever the prompt."""
+    cfg = gpt2.GPT2Config()
+    sd = gpt2.random_state_dict(cfg, seed=21)
+    gen = torch.Generator().manual_seed(21)
+    bias = torch.randn(cfg.n_embd, generator=gen)                 # ln_f.bias: a fixed direction in every position
+    sd["transformer.ln_f.bias"] = bias.half()
+    unit = sd["transformer.ln_f.bias"].float()
+    unit = unit / unit.dot(unit)
+    planted = [40000, 7, 31337, 12345, 50256]
+    for rank, tok in enumerate(planted):                          # logit contribution 80, 68, 56, 44, 32
+        sd["transformer.wte.weight"][tok] = (sd["transformer.wte.weight"][tok].float() + (80 - 12 * rank) * unit).half()
+    ids = torch.randint(0, cfg.vocab_size, (2, 64), generator=gen)
+    runner = gpt2.GPT2Runner(cfg, sd, device=dev)
+    logits = runner.forward(ids.to(dev), check_ids=True).cpu()
+    ref = O.torch_gpt2(sd, cfg.n_layer, cfg.n_head, cfg.layer_norm_epsilon, ids)
+    assert torch.topk(ref[0, -1], 5).indices.tolist() == planted  # the construction works on the oracle side
+    assert gpt2.top5_match(logits, ref) == (True, True)           # the strict rule, unconditionally
+    l16 = runner.forward(ids.to(dev), logits_dtype=torch.float16, last_only=True).cpu()
+    assert gpt2.top5_match(l16, ref) == (True, True)
+    assert hexb200.device_status() == 0
+
+
+def test_gpt2_rejects_out_of_range_ids_when_asked():
+    cfg = gpt2.GPT2Config()
+    runner = gpt2.GPT2Runner(cfg, gpt2.random_state_dict(cfg, seed=3), device=dev)
+    ids = torch.randint(0, cfg.vocab_size, (1, 16), generator=torch.Generator().manual_seed(1))
+    ids[0, 3] = cfg.vocab_size                                     # one past the end
+    with pytest.raises(IndexError):
+        runner.forward(ids.to(dev), check_ids=True)
+    with pytest.raises(IndexError):
+        ops.embedding(runner.w["transformer.wte.weight"], runner.w["transformer.wpe.weight"], ids.to(dev),
+                      torch.empty(1, 16, cfg.n_embd, dtype=torch.float16, device=dev), check_ids=True)
+    assert hexb200.device_status() == 0                            # nothing was launched
+
+
 def test_gpt2_graph_replay_matches_eager():
     cfg = gpt2.GPT2Config()
     runner = gpt2.GPT2Runner(cfg, gpt2.random_state_dict(cfg, seed=5), device=dev)

@@ -146,6 +146,55 @@ def test_layer_norm_vs_oracle(dev, rows, cols, dtype):
     assert torch.allclose(rstd, 1.0 / torch.sqrt(xf.var(dim=1, unbiased=False) + 1e-5), rtol=1e-3)
 
 
+def ulp_distance_f16(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Distance between two fp16 tensors in units in the last place (ordered-integer view of the bits)."""
+    def ordered(t):
+        i = t.contiguous().view(torch.int16).to(torch.int32)
+        return torch.where(i >= 0, i, -(i & 0x7FFF))
+    return (ordered(a) - ordered(b)).abs()
+
+
+def assert_within_ulps(got, ref, max_ulps, max_mismatch_fraction, tiny):
+    """Every element within max_ulps fp16 ulps of ref, or -- for results so close to zero that an ulp
+    is smaller than the fp32 round-off of the inputs to the final rounding -- within `tiny` absolutely."""
+    d = ulp_distance_f16(got, ref)
+    bad = (d > max_ulps) & ((got.float() - ref.float()).abs() > tiny)
+    assert int(bad.sum()) == 0, f"{int(bad.sum())} elements beyond {max_ulps} ulp, worst {int(d.max())}"
+    assert float((d > 0).float().mean()) < max_mismatch_fraction
+
+
+@pytest.mark.parametrize("affine_f32", [1, 0])
+def test_layer_norm_config2_within_one_ulp_of_the_oracle(dev, affine_f32):
+    """Configuration 2 at full size, element by element against the C oracle (fp32 arithmetic from the
+    fp16 inputs, one rounding): the kernel that does the affine step in fp32 differs by at most one
+    fp16 ulp anywhere (a different summation order can move a value across a rounding boundary), and
+    in few places; the packed-fp16 affine variant rounds twice and may be two ulps off."""
+    x, w, b = O.make_layer_norm_inputs()                           # [16384 x 4096] fp16
+    hexb200.set_option("norm_affine_f32", affine_f32)
+    try:
+        y, mean, rstd = gpu_layer_norm(x, w, b, 1e-5, dev)
+    finally:
+        hexb200.set_option("norm_affine_f32", 1)
+    yc, mc, rc = O.c_layer_norm(x, w, b, 1e-5)
+    assert_within_ulps(y, yc, 1 if affine_f32 else 2, 0.01 if affine_f32 else 0.3, tiny=5e-7)
+    assert torch.allclose(mean, mc, atol=1e-6) and torch.allclose(rstd, rc, rtol=1e-5)
+
+
+@pytest.mark.parametrize("affine_f32", [1, 0])
+def test_rms_norm_decoder_shape_within_one_ulp_of_the_oracle(dev, affine_f32):
+    """The decoder's RMSNorm shape [8192 x 2048] fp16 (eight launches per forward pass), same bar."""
+    g = torch.Generator().manual_seed(4242)
+    x = torch.randn(8192, 2048, generator=g).half()
+    gain = (0.5 + torch.rand(2048, generator=g)).half()
+    xd, y = x.to(dev), torch.empty(8192, 2048, dtype=torch.float16, device=dev)
+    hexb200.set_option("norm_affine_f32", affine_f32)
+    try:
+        ops.rms_norm(xd, y, gain.to(dev), eps=1e-6)
+    finally:
+        hexb200.set_option("norm_affine_f32", 1)
+    assert_within_ulps(y.cpu(), O.c_rms_norm(x, gain, 1e-6), 1 if affine_f32 else 2, 0.01 if affine_f32 else 0.3, tiny=5e-7)
+
+
 def test_layer_norm_without_stats_and_reference_dtype_stats(dev):
     x, w, b = O.make_layer_norm_inputs(64, 1024, torch.float16)
     y0, _, _ = gpu_layer_norm(x, w, b, 1e-5, dev, stats=False)
@@ -267,10 +316,10 @@ def test_matmul_full_size_properties(dev):
     # linearity in A: (2A) B == 2 (A B) up to the last fp16 bit (power-of-two scaling)
     ops.matmul(ad * 2, bd, c2)
     assert O.max_rel_err(c2.float(), c.float() * 2) < 1e-3
-    # sampled rows against the oracle
-    rows = torch.tensor([0, 1, 127, 128, 2047, 4095])
-    ref = O.torch_matmul(a[rows], b)
-    assert O.max_rel_err(c[rows.to(dev)].cpu(), ref) < REL_F16
+    # the whole 4096 x 4096 output against torch CPU (fp32 arithmetic from the fp16 inputs, one rounding)
+    ref = O.torch_matmul(a, b)
+    assert O.max_rel_err(c.cpu(), ref) < REL_F16
+    assert_within_ulps(c.cpu(), ref, 1, 0.05, tiny=2e-4)           # fp32 accumulation in another order
     # checksum: column sums of C == (column sums of A) B
     colsum = c.float().sum(dim=0).cpu()
     ref_sum = (a.float().sum(dim=0, keepdim=True) @ b.float()).squeeze(0)
@@ -355,8 +404,8 @@ def test_attention_full_size_properties(dev):
     ones = torch.ones_like(vd)
     ops.attention(qd, kd, ones, o2, causal=True)
     assert (o2.float() - 1).abs().max().item() < 2e-3
-    # sampled heads against the oracle
-    for (z, h) in ((0, 0), (3, 31), (1, 17)):
+    # heads spread over every batch index and the head range against the oracle
+    for (z, h) in ((0, 0), (0, 13), (1, 17), (1, 30), (2, 5), (2, 22), (3, 9), (3, 31)):
         ref = O.torch_attention(q[z:z + 1, h:h + 1], k[z:z + 1, h:h + 1], v[z:z + 1, h:h + 1], 128 ** -0.5, True)
         assert O.max_rel_err(o[z:z + 1, h:h + 1].cpu(), ref) < REL_F16
     assert hexb200.device_status() == 0
@@ -420,6 +469,42 @@ def test_decoder_config5_one_sequence(dev):
     stack2.forward(x2, out2)
     assert torch.equal(out2[0], out2[1])
     assert torch.equal(out2[0], out[0])
+
+
+def test_decoder_config5_batch8_three_sequences(dev):
+    """Configuration 5 as benchmarked (batch 8 x 1024 tokens): the first, a middle and the last
+    sequence of the output against the torch CPU oracle run on those sequences alone."""
+    x, ws = O.make_decoder_inputs(4, 2048, 16, 8192, 8, 1024)
+    wd = [{k: v.to(dev) for k, v in w.items()} for w in ws]
+    stack = ops.DecoderStack(wd, 16, 128, 8192, 8, 1024, 1e-6)
+    out = torch.empty(8, 1024, 2048, dtype=torch.float16, device=dev)
+    stack.forward(x.to(dev), out)
+    torch.cuda.synchronize()
+    assert hexb200.device_status() == 0
+    got = out.cpu()
+    for b in (0, 3, 7):
+        ref = O.torch_decoder(x[b:b + 1].contiguous(), ws, 16, 128, 8192, 1, 1024, 1e-6)
+        assert O.max_rel_err(got[b:b + 1], ref) < REL_F16, b
+
+
+# ------------------------------------------------------------------ bounded waits
+def test_bounded_wait_runs_out_and_the_context_stays_usable(dev):
+    """A device-side wait that nothing satisfies gives up after its limit: the call returns, the status
+    word reports HEXB_ERR_TIMEOUT exactly once, and a tensor-core matmul afterwards is still right."""
+    import time
+    lib = hexb200.load()
+    assert hexb200.device_status() == 0
+    assert lib.hexb_selftest_bounded_wait(0, None) == -1            # limit out of range: nothing is launched
+    t = time.perf_counter()
+    assert lib.hexb_selftest_bounded_wait(1000, torch.cuda.current_stream().cuda_stream) == 0   # 1 ms
+    assert lib.hexb_status_string(hexb200.device_status()).decode() == "HEXB_ERR_TIMEOUT"
+    assert time.perf_counter() - t < 1.0                            # far below the kernels' 2 s default
+    assert hexb200.device_status() == 0                             # reported once, then clear
+    a, b = O.make_matmul_inputs(512, 512, 256, seed=5)
+    c = torch.empty(512, 512, dtype=torch.float16, device=dev)
+    ops.matmul(a.to(dev), b.to(dev), c)
+    assert O.max_rel_err(c.cpu(), O.torch_matmul(a, b)) < REL_F16
+    assert hexb200.device_status() == 0
 
 
 # ------------------------------------------------------------------ host-buffer entry points and errors
@@ -608,18 +693,29 @@ def test_attention_additive_causal_mask_equals_causal_flag(dev, D):
     assert hexb200.device_status() == 0
 
 
-def test_attention_fully_masked_row_is_nan_like_the_reference(dev):
+@pytest.mark.parametrize("D,force_simt", [(64, 0), (128, 0), (64, 1), (48, 0)])
+def test_attention_fully_masked_row_is_nan_like_the_reference(dev, D, force_simt):
+    """A row whose keys are all masked to -inf is NaN (exp(-inf - -inf)), on the tensor-core kernel and on
+    the CUDA-core kernel alike (D = 48 and the forced case take the latter); a row whose FIRST key blocks
+    are masked out but later ones are not is finite and right; every other row matches the oracle."""
     g = torch.Generator().manual_seed(4)
-    q, k, v = (torch.randn(1, 1, 128, 64, generator=g).half().to(dev) for _ in range(3))
-    mask = torch.zeros(128, 128)
+    q, k, v = (torch.randn(1, 1, 192, D, generator=g).half() for _ in range(3))
+    mask = torch.zeros(192, 192)
     mask[5, :] = float("-inf")
-    out = torch.empty(1, 1, 128, 64, dtype=torch.float32, device=dev)
-    ops.attention_ex(q, k, v, out, mask=mask.to(dev))
+    mask[9, :130] = float("-inf")                # two whole 64-key blocks and a bit: weights 0 there, not NaN
+    out = torch.empty(1, 1, 192, D, dtype=torch.float32, device=dev)
+    hexb200.set_option("attn_force_simt", force_simt)
+    try:
+        ops.attention_ex(q.to(dev), k.to(dev), v.to(dev), out, mask=mask.to(dev))
+    finally:
+        hexb200.set_option("attn_force_simt", 0)
     o = out.cpu()[0, 0]
     assert torch.isnan(o[5]).all()
-    keep = torch.ones(128, dtype=torch.bool)
+    keep = torch.ones(192, dtype=torch.bool)
     keep[5] = False
     assert torch.isfinite(o[keep]).all()
+    ref = _sdpa_ref(q, k, v, mask.view(1, 1, 192, 192), 1.0 / math.sqrt(D))[0, 0]
+    assert O.max_rel_err(o[keep], ref[keep]) < REL_F16
 
 
 def test_attention_masked_odd_strides_and_broadcast(dev):

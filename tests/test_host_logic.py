@@ -39,7 +39,9 @@ def test_split_options_warns_on_option_like_typos_and_rejects_unknowns():
 
 
 def test_option_field_list_matches_the_reference_dataclass():
-    ref = os.path.join(os.environ.get("HEXAGON_MLIR_REF", "/root/reference"), "qcom_hexagon_backend/backend/hexagon_options.py")
+    if not os.environ.get("HEXAGON_MLIR_REF"):
+        pytest.skip("set HEXAGON_MLIR_REF to a checkout of the reference to run this check")
+    ref = os.path.join(os.environ["HEXAGON_MLIR_REF"], "qcom_hexagon_backend/backend/hexagon_options.py")
     if not os.path.exists(ref):
         pytest.skip("reference checkout not present")
     import re
@@ -153,37 +155,99 @@ def _free_port():
     return port
 
 
-def _rank_main(rank, world, port, rows, cols, q):
+def _cpu_compute(name, O):
+    """Stand-ins for the per-GPU kernels: the oracle's CPU calls on the rank's block."""
+    if name == "softmax":
+        return lambda x: O.torch_softmax(x)
+    if name == "layernorm":
+        return lambda x, weight, bias: O.torch_layer_norm(x, weight, bias, 1e-5)
+    if name == "gemm":
+        return lambda a, b: O.torch_matmul(a, b)
+    if name == "attention":
+        return lambda q, k, v: (O.torch_attention(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), q.shape[-1] ** -0.5, True)[0]
+                                if q.shape[0] else q.clone())
+    if name == "decoder":
+        def run(x, weights):
+            if x.shape[0] == 0:
+                return x.clone()
+            d, ff = weights[0]["wo"].shape[0], weights[0]["wd"].shape[0]
+            return O.torch_decoder(x.contiguous(), weights, 2, d // 2, ff, x.shape[0], x.shape[1], 1e-6)
+        return run
+    raise KeyError(name)
+
+
+def _small_inputs(name, units, O):
+    """The five configurations at toy sizes with `units` partition units (same seeds on every rank)."""
+    if name == "softmax":
+        return {"x": O.make_softmax_inputs(units, 32, seed=77)}
+    if name == "layernorm":
+        x, w, b = O.make_layer_norm_inputs(units, 64, seed=78)
+        return {"x": x, "weight": w, "bias": b}
+    if name == "gemm":
+        a, b = O.make_matmul_inputs(units, 24, 16, seed=79)
+        return {"a": a, "b": b}
+    if name == "attention":
+        q, k, v = O.make_attention_inputs(1, units, 16, 8, seed=80)
+        return {"q": q, "k": k, "v": v}
+    x, ws = O.make_decoder_inputs(1, 16, 2, 32, units, 8, seed=81)
+    return {"x": x, "weights": ws}
+
+
+def _rank_main(rank, world, port, units, q):
     sys.path.insert(0, ROOT)
+    from hexb200.dist import PARTITIONS, run_partitioned
     from oracle import oracle as O
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        x = O.make_softmax_inputs(rows, cols, seed=77)            # every rank draws the same matrix
-        mine = shard_rows(x, world, rank)
-        y_local = O.torch_softmax(mine)                           # stand-in for the per-GPU kernel
-        y = all_gather_rows(y_local, rows)
-        ok = torch.allclose(y, O.torch_softmax(x), atol=1e-7)
-        q.put((rank, bool(ok), tuple(y.shape)))
+        res = {}
+        for name in PARTITIONS:
+            inputs = _small_inputs(name, units, O)                       # every rank draws the same tensors
+            y = run_partitioned(name, inputs, _cpu_compute(name, O), world, rank)   # shard -> compute -> gather
+            whole = run_partitioned(name, inputs, _cpu_compute(name, O), 1, 0, gather=False)
+            if name == "attention":
+                whole = whole.reshape(y.shape)
+            res[name] = (bool(torch.allclose(y.float(), whole.float(), atol=1e-6)), tuple(y.shape))
+        q.put((rank, res))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("rows", [64, 37])
-def test_two_rank_shard_and_gather_gloo(rows):
+@pytest.mark.parametrize("units", [6, 5, 1])
+def test_two_rank_shard_compute_gather_gloo(units):
+    """The function the benchmark's multi-GPU leg uses (run_partitioned), on two CPU ranks over gloo,
+    for all five configurations, with even, ragged and fewer-units-than-ranks partitions."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, rows, 32, q)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, units, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=120) for _ in procs]
+    res = [q.get(timeout=180) for _ in procs]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    assert all(ok for _, ok, _ in res)
-    assert all(shape == (rows, 32) for _, _, shape in res)
+    for _, per_name in res:
+        for name, (ok, shape) in per_name.items():
+            assert ok, name
+            assert shape[0] == (1 if name == "attention" else units), (name, shape)
+
+
+def test_partition_rejects_missing_operands_and_samples_every_rank():
+    from hexb200.dist import partition, sample_units, units_of
+
+    with pytest.raises(KeyError):
+        partition("layernorm", {"x": torch.zeros(4, 4)}, 2, 0)
+    q = torch.zeros(2, 3, 4, 8)
+    assert units_of("attention", {"q": q}) == 6
+    assert partition("attention", {"q": q, "k": q, "v": q}, 4, 3)["q"].shape == (1, 4, 8)
+    for total, world in ((16384, 8), (128, 8), (8, 8), (3, 2), (1, 4)):
+        picks = sample_units(total, world)
+        owners = set()
+        for u in picks:
+            owners |= {r for r in range(world) if shard_range(total, world, r)[0] <= u < sum(shard_range(total, world, r))}
+        assert owners == {r for r in range(world) if shard_range(total, world, r)[1] > 0}
 
 
 def test_raw_tensor_file_round_trip(tmp_path):
