@@ -22,7 +22,7 @@
 //
 // A CUDA-core kernel covers fp32 tensors (the dtype of the reference's Triton test) and head
 // sizes / strides the TMA path cannot take.
-#include "tc_sm100.cuh"
+#include "attn_common.cuh"
 
 namespace hexb {
 
@@ -33,7 +33,6 @@ namespace attn {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_N = 128;
 constexpr int THREADS = 192;
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 template <int HD>
 struct Cfg {
@@ -46,71 +45,6 @@ struct Cfg {
   static constexpr int TMEM_COLS = 256;              // S: [0,128)  (P aliases [0,64));  O: [128,128+HD)
   static constexpr int O_COL = 128;
 };
-
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// 2^x on the FMA pipe: x = n + f with n = round(x) taken from the mantissa of x + 1.5*2^23,
-// 2^f by a degree-3 polynomial on [-0.5, 0.5] (max relative error 7.5e-5, below the fp16 rounding
-// of P), exponent patched in with an integer add.  Used for a fraction of the exponentials so the
-// special-function unit is not the only path they go through.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -126.0f);
-  const float t = x + 12582912.0f;
-  const float f = x - (t - 12582912.0f);
-  float r = fmaf(0.05517161265015602f, f, 0.2426111251115799f);
-  r = fmaf(r, f, 0.6932609677314758f);
-  r = fmaf(r, f, 0.9999280571937561f);
-  return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
-}
-// Measured on B200 ([4,32,4096,128] causal): 0 -> 614 us, 4 -> 649 us.  The softmax warps are
-// bound by instruction issue before the special-function unit, so the offload stays off.
-constexpr int kPolyEvery = 0;  // one exponential in kPolyEvery goes through ex2_poly (0 = none)
-
-// Two fp32 lanes per instruction (sm_100 packed arithmetic): halves the issue slots of the scale-and-
-// shift and of the row-sum in the softmax loop, which is bound by instruction issue.
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-  float2 d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;"
-      : "=l"(reinterpret_cast<unsigned long long &>(d))
-      : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)),
-        "l"(reinterpret_cast<unsigned long long &>(c)));
-  return d;
-}
-__device__ __forceinline__ float2 add2(float2 a, float2 b) {
-  float2 d;
-  asm("add.rn.f32x2 %0, %1, %2;"
-      : "=l"(reinterpret_cast<unsigned long long &>(d))
-      : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)));
-  return d;
-}
-
-// {lo, hi} -> packed fp16 pair (lo in bits 0..15)
-__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-
-// Phase timing for development builds (-DHEXB_ATTN_PROFILE): clock64 stamps around the phases of
-// one softmax warp and of the MMA thread of attn_fwd_tc2_kernel, summed into a device buffer that
-// hexb_debug_set_attn_profile() registers.  Compiled out otherwise.
-#ifdef HEXB_ATTN_PROFILE
-#define HEXB_PROF_DECL(n) long long prof_t[n] = {}; long long prof_last = clock64();
-#define HEXB_PROF(i) { const long long now_ = clock64(); prof_t[i] += now_ - prof_last; prof_last = now_; }
-#define HEXB_PROF_FLUSH(base, n) if (p.prof) { for (int i_ = 0; i_ < n; ++i_) atomicAdd(p.prof + base + i_, (unsigned long long)prof_t[i_]); }
-#else
-#define HEXB_PROF_DECL(n)
-#define HEXB_PROF(i)
-#define HEXB_PROF_FLUSH(base, n)
-#endif
 
 struct Params {
 #ifdef HEXB_ATTN_PROFILE
@@ -853,6 +787,9 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #ifdef HEXB_ATTN_PROFILE
 static unsigned long long *g_attn_prof = nullptr;
 extern "C" void hexb_debug_set_attn_profile(void *dev_buf) { g_attn_prof = (unsigned long long *)dev_buf; }
+}  // namespace attn
+unsigned long long *attn_profile_buffer() { return attn::g_attn_prof; }
+namespace attn {
 #endif
 
 // CUDA-core forward for fp32 tensors and for shapes the TMA path cannot take: one warp per query
@@ -935,15 +872,6 @@ attn_fwd_simt_kernel(const T *__restrict__ Q, const T *__restrict__ K, const T *
   }
 }
 
-// Optional parts of a forward call: key length, output type, additive mask.
-struct Extra {
-  int64_t n_kv;
-  int out_f32;
-  const void *mask;
-  int mask_f32;
-  int64_t sm[3];
-};
-
 template <typename T>
 static int launch_simt(const T *Q, const T *K, const T *V, void *O, int64_t Z, int64_t H, int64_t N,
                        int64_t D, const int64_t *s, float scale_log2, int causal, const Extra &x,
@@ -971,7 +899,7 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   using cfg = Cfg<HD>;
   // 2: 64-key blocks, two score buffers; 1: 128-key blocks (plain calls only)
   const bool plain = !x.mask && !x.out_f32 && x.n_kv == N;
-  const int which = (int)option(OPT_attn_kernel, 2);
+  const int which = (int)option(OPT_attn_kernel, 0);
   const bool two_buffers = !plain || which != 1;
   const bool wide = two_buffers && !x.mask && which == 5;  // 128-key blocks, one CTA per SM
   CUtensorMap tm[4];
@@ -1060,10 +988,11 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
 }  // namespace attn
 
 int attn_device_status_fetch_and_clear(int *out) {
-  int v = 0, zero = 0;
+  int v = 0, zero = 0, v3 = 0;
   HEXB_CUDA_OK(cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int)));
   if (v) HEXB_CUDA_OK(cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int)));
-  *out = v;
+  if (int e = attn_pingpong_status_fetch_and_clear(&v3)) return e;
+  *out = v ? v : v3;
   return HEXB_OK;
 }
 
@@ -1094,6 +1023,14 @@ static int attention_f16_dispatch(const void *Q, const void *K, const void *V, v
   bool tma_ok = (D == 64 || D == 128) && !option(OPT_attn_force_simt, 0) && aligned16(Q) && aligned16(K) &&
                 aligned16(V);
   for (int i = 0; i < 9 && tma_ok; ++i) tma_ok = s[i] % 8 == 0 && s[i] > 0;
+  // attn_kernel: 0 or 2 = 64-key blocks with two score buffers (the default), 1 = 128-key blocks / one score
+  // buffer, 3 = two query tiles per persistent CTA taking turns (attention_pingpong.cu), 5 = 128-key blocks /
+  // two score buffers / one CTA per SM
+  const int which = (int)option(OPT_attn_kernel, 0);
+  const bool plain = !x.mask && x.n_kv == N;
+  if (tma_ok && plain && which == 3 && attn_pingpong_supported(Z, H, N, D, causal, di.sm_count))
+    return attn_pingpong_launch((const __half *)Q, (const __half *)K, (const __half *)V, Out, Z, H, N, D, s, scale_log2,
+                                causal, x.out_f32, st);
   if (tma_ok) {
     if (D == 128)
       return attn::launch_tc<128>((const __half *)Q, (const __half *)K, (const __half *)V, Out, Z, H, N, s,
