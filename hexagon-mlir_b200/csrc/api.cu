@@ -79,6 +79,8 @@ int current_device(DeviceInfo *out) {
     cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev);
     cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     d.smem_optin = (size_t)v;
+    cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev);
+    d.l2_bytes = (size_t)v;
     d.device = dev;
   }
   *out = d;

@@ -23,7 +23,7 @@ int check_launch(const char *where);  // cudaGetLastError -> status
   X(softmax_vpt_max) X(softmax_force_stream) X(softmax_ring) X(softmax_bulk_store) X(norm_ring)      \
   X(norm_bulk_store) X(ring_bytes_per_warp) X(ring_map) X(norm_vpt_max) X(norm_force_stream)         \
   X(norm_ctas_per_sm) X(norm_affine_f32) X(gemm_bn) X(gemm_tail_split) X(gemm_pair) X(gemm_epi_warps) \
-  X(gemm_tma_store) X(gemm_force_simt) X(attn_force_simt) X(attn_tiles_per_cta) X(attn_kernel)       \
+  X(gemm_tma_store) X(gemm_group_m) X(gemm_force_simt) X(attn_force_simt) X(attn_tiles_per_cta) X(attn_kernel)       \
   X(attn_mask_tma) X(scan_force_scalar) X(scan_segments) X(scan_kv) X(decoder_fused_swiglu)          \
   X(host_chunks) X(pdl) X(tmap_cache) X(wait_limit_us)
 // Descriptor-field overrides that can mis-describe an operand: compiled in only
@@ -57,6 +57,7 @@ struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0, cc_minor = 0;
   size_t smem_optin = 0;
+  size_t l2_bytes = 0;
 };
 // Properties of the current device (cached per device id); status != HEXB_OK if there is none.
 int current_device(DeviceInfo *out);

@@ -22,6 +22,40 @@ namespace hexb {
 
 static __device__ int g_gemm_status = 0;
 
+// ---- tile order.  Tiles are walked in groups of `group_m` row-tiles: inside a group the row-tile index
+// runs fastest, then the column-tile index, then the next group.  The tiles that run at the same time
+// then share `group_m` row-blocks of A and about (concurrent tiles / group_m) column-blocks of B.
+// group_m == tiles_m is the plain column-tile-major order: right when A and B both stay in L2 anyway.
+__host__ __device__ __forceinline__ void tile_to_mn(int tile, int tiles_m, int tiles_n, int group_m, int *tm, int *tn) {
+  const int per_group = group_m * tiles_n;
+  const int g = tile / per_group, r = tile - g * per_group;
+  const int first = g * group_m;
+  const int gsize = tiles_m - first < group_m ? tiles_m - first : group_m;
+  *tn = r / gsize;
+  *tm = first + (r - *tn * gsize);
+}
+
+// Chooses group_m so that the operand blocks of the tiles in flight (`concurrent` of them, each reading
+// a_tile_bytes of A and b_tile_bytes of B over the whole K) fit L2: minimise
+// group_m * a_tile + ceil(concurrent / group_m) * b_tile.  When all of A and B fit anyway the plain order
+// is kept.  Measured on [8192 x 8192] x [8192 x 2048] (the decoder's down projection: A is 128 MiB, more
+// than L2): the plain order re-reads A from DRAM in every wave.
+static int choose_group_m(int tiles_m, int tiles_n, int concurrent, double a_tile_bytes, double b_tile_bytes, size_t l2_bytes) {
+  const int forced = option(OPT_gemm_group_m, 0);
+  if (forced > 0) return forced < tiles_m ? forced : tiles_m;
+  const double l2 = l2_bytes ? (double)l2_bytes : 100e6;
+  if (tiles_m * a_tile_bytes + tiles_n * b_tile_bytes <= 0.85 * l2) return tiles_m;
+  int best = tiles_m;
+  double best_ws = 1e30;
+  for (int g = 1; g <= tiles_m; ++g) {
+    const int cols = (concurrent + g - 1) / g;
+    const double ws = g * a_tile_bytes + (cols < tiles_n ? cols : tiles_n) * b_tile_bytes;
+    if (ws < best_ws) { best_ws = ws; best = g; }
+  }
+  return best;
+}
+
+
 namespace gemm {
 
 constexpr int BM = 128;
@@ -321,7 +355,7 @@ template <int BN, int STAGES, typename OutT, int EPI = 0, bool BT = false>
 __global__ void __launch_bounds__(MAX_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
-               int64_t ldr, int tiles_m, int tiles_n, int vec_ok, uint32_t b_lbo, uint32_t b_sbo,
+               int64_t ldr, int tiles_m, int tiles_n, int group_m, int vec_ok, uint32_t b_lbo, uint32_t b_sbo,
                int full_items, int split, const EpiArgs epi, const __grid_constant__ CUtensorMap tmC, int use_tma,
                int r_vec) {
   using cfg = Cfg<BN, STAGES>;
@@ -387,8 +421,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       sub = k - (k / split) * split;
       it.width = BN / split;
     }
-    it.tm = tile % tiles_m;
-    it.col0 = (tile / tiles_m) * (EPI == 1 ? BN / 2 : BN) + sub * it.width;
+    int tn;
+    tile_to_mn(tile, tiles_m, tiles_n, group_m, &it.tm, &tn);
+    it.col0 = tn * (EPI == 1 ? BN / 2 : BN) + sub * it.width;
     return it;
   };
 
@@ -543,7 +578,7 @@ template <typename OutT, int EPI, bool BT = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MAX_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     OutT *__restrict__ C, const __half *__restrict__ R, int M, int N, int K, int64_t ldc,
-                    int64_t ldr, int tiles_m, int tiles_n, int vec_ok, const EpiArgs epi,
+                    int64_t ldr, int tiles_m, int tiles_n, int group_m, int vec_ok, const EpiArgs epi,
                     const __grid_constant__ CUtensorMap tmC, int use_tma, int r_vec, int full_items, int split) {
   using namespace pair;
   extern __shared__ uint8_t smem_raw[];
@@ -609,8 +644,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       sub = k - (k / split) * split;
       it.width = BN / split;
     }
-    it.tm = tile % tiles_m;
-    it.col0 = (tile / tiles_m) * OUT_COLS + sub * it.width;
+    int tn;
+    tile_to_mn(tile, tiles_m, tiles_n, group_m, &it.tm, &tn);
+    it.col0 = tn * OUT_COLS + sub * it.width;
     return it;
   };
 
@@ -744,7 +780,7 @@ static StoreMap make_store_map(OutT *C, const __half *R, int64_t M, int64_t N, i
 
 template <typename OutT, int EPI, bool BT = false>
 static int launch_tc_pair(const EpiArgs &epi, const StoreMap &sm, const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M, int N,
-                          int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count, cudaStream_t st) {
+                          int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count, size_t l2_bytes, cudaStream_t st) {
   static PerDeviceOnce attr_done;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -768,15 +804,16 @@ static int launch_tc_pair(const EpiArgs &epi, const StoreMap &sm, const CUtensor
   }
   const int items = full_items + (tiles - full_items) * split;
   const int clusters = items < max_clusters ? items : max_clusters;
+  const int group_m = choose_group_m(tiles_m, tiles_n, clusters, 256.0 * K * 2, (EPI == 1 ? 2.0 : 1.0) * OUT_COLS * K * 2, l2_bytes);
   launch_pdl(kern, dim3(2 * clusters), dim3(launch_threads(M, N, K, EPI == 1 ? 1 : epi.act, sm_count)),
-             (size_t)pair::SMEM_BYTES, st, tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok, epi, sm.tm, sm.use,
-             sm.r_vec, full_items, split);
+             (size_t)pair::SMEM_BYTES, st, tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, group_m, vec_ok, epi, sm.tm,
+             sm.use, sm.r_vec, full_items, split);
   return check_launch("gemm_tc_pair");
 }
 
 template <int BN, int STAGES, typename OutT, int EPI = 0, bool BT = false>
 static int launch_tc(const EpiArgs &epi, const StoreMap &sm, const CUtensorMap &tmA, const CUtensorMap &tmB, OutT *C, const __half *R, int M,
-                     int N, int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count,
+                     int N, int K, int64_t ldc, int64_t ldr, int vec_ok, int sm_count, size_t l2_bytes,
                      cudaStream_t st) {
   using cfg = Cfg<BN, STAGES>;
   static PerDeviceOnce attr_done;
@@ -801,9 +838,10 @@ static int launch_tc(const EpiArgs &epi, const StoreMap &sm, const CUtensorMap &
   const int grid = items < sm_count ? items : sm_count;
   const uint32_t lbo = (uint32_t)HEXB_DEV_OPTION(OPT_gemm_b_lbo, BK * 128);
   const uint32_t sbo = (uint32_t)HEXB_DEV_OPTION(OPT_gemm_b_sbo, 1024);
+  const int group_m = choose_group_m(tiles_m, tiles_n, grid, (double)BM * K * 2, (EPI == 1 ? 2.0 : 1.0) * OUT_COLS * K * 2, l2_bytes);
   launch_pdl(kern, dim3(grid), dim3(launch_threads(M, N, K, EPI == 1 ? 1 : epi.act, sm_count)), (size_t)cfg::SMEM_BYTES, st,
-             tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, vec_ok, lbo, sbo, full_items, split, epi, sm.tm, sm.use,
-             sm.r_vec);
+             tmA, tmB, C, R, M, N, K, ldc, ldr, tiles_m, tiles_n, group_m, vec_ok, lbo, sbo, full_items, split, epi, sm.tm,
+             sm.use, sm.r_vec);
   return check_launch("gemm_tc");
 }
 
@@ -855,15 +893,15 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
   // CTA-pair kernel for problems with at least one 256 x 256 tile per pair of SMs
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
   if (option(OPT_gemm_bn, 0) == 0 && option(OPT_gemm_pair, 1) && pair_tiles >= di.sm_count / 2)
-    return launch_tc_pair<OutT, EPI, BT>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+    return launch_tc_pair<OutT, EPI, BT>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, di.l2_bytes, st);
   if (BT && bn == 64) bn = 128;  // the transposed form loads Bt in 128-row boxes
   switch (bn) {
     case 64:
-      return launch_tc<64, 8, OutT, EPI, false>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<64, 8, OutT, EPI, false>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, di.l2_bytes, st);
     case 128:
-      return launch_tc<128, 6, OutT, EPI, BT>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<128, 6, OutT, EPI, BT>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, di.l2_bytes, st);
     default:
-      return launch_tc<256, 4, OutT, EPI, BT>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, st);
+      return launch_tc<256, 4, OutT, EPI, BT>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, di.l2_bytes, st);
   }
 }
 
@@ -969,9 +1007,9 @@ extern "C" int hexb_matmul_swiglu_f16(const void *A, const void *B_gate_up, void
   const gemm::StoreMap sm = gemm::make_store_map<__half>((__half *)out, nullptr, M, F, ldo, ldo, tmA);
   if (option(OPT_gemm_pair, 1) && ((M + 255) / 256) * ((F + 127) / 128) >= di.sm_count / 2)
     return launch_tc_pair<__half, 1>(gemm::EpiArgs{nullptr, 0}, sm, tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
-                                     di.sm_count, (cudaStream_t)stream);
+                                     di.sm_count, di.l2_bytes, (cudaStream_t)stream);
   return launch_tc<256, 4, __half, 1>(gemm::EpiArgs{nullptr, 0}, sm, tmA, tmB, (__half *)out, nullptr, (int)M, (int)F, (int)K, ldo, ldo, vec_ok,
-                                      di.sm_count, (cudaStream_t)stream);
+                                      di.sm_count, di.l2_bytes, (cudaStream_t)stream);
 }
 
 extern "C" int hexkl_matmul_f16f16_f32(int64_t n_row, int64_t n_col, int64_t n_inner, float *outM,

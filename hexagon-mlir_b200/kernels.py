@@ -194,16 +194,17 @@ class KernelLauncher:
         self.name = name
         self.__name__ = name
         self._impl = impl
-        self._sig = inspect.signature(impl)
-        self._params = list(self._sig.parameters)
+        self._params = frozenset(inspect.signature(impl).parameters)
+        self._wants_grid = "_grid" in self._params
 
     def __getitem__(self, grid):
+        impl, params, wants_grid = self._impl, self._params, self._wants_grid
+
         def run(*args, **kwargs):
-            kargs, _opts = split_options(kwargs, self._params)
-            if "_grid" in self._params:
+            kargs, _opts = split_options(kwargs, params)
+            if wants_grid:
                 kargs["_grid"] = grid
-            bound = self._sig.bind(*args, **kargs)
-            self._impl(*bound.args, **bound.kwargs)
+            impl(*args, **kargs)      # Python's own binding raises TypeError for a wrong argument list
             return None
 
         return run

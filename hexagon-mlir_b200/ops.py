@@ -25,8 +25,38 @@ def _dt(t: torch.Tensor) -> int:
     return _DT[t.dtype]
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(t: torch.Tensor) -> int:
+    """The raw cudaStream_t of torch's current stream on the tensor's device."""
+    if _raw_stream is not None:
+        idx = t.device.index
+        return _raw_stream(torch.cuda.current_device() if idx is None else idx)
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class _guard:
+    """Makes `dev` the current CUDA device for the duration of a call; costs one query when it already is
+    (the usual case), where torch.cuda.device() always pays a set/restore pair."""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, dev: torch.device):
+        self.idx = dev.index
+        self.prev = -1
+
+    def __enter__(self):
+        if self.idx is not None:
+            cur = torch.cuda.current_device()
+            if cur != self.idx:
+                self.prev = cur
+                torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def _ptr(t):
@@ -57,7 +87,7 @@ def softmax(x: torch.Tensor, out: torch.Tensor) -> None:
     if (rows, cols) != (r2, c2) or x.dtype != out.dtype:
         raise ValueError("softmax: x and out differ in shape or dtype")
     if dev.type == "cuda":
-        with torch.cuda.device(dev):
+        with _guard(dev):
             fn = lib.hexb_softmax_f16 if x.dtype == torch.float16 else lib.hexb_softmax_f32
             _dt(x)
             check(fn(_ptr(x), _ptr(out), rows, cols, xs, ys, _stream(x)), "softmax")
@@ -91,7 +121,7 @@ def layer_norm(x, out, weight, bias, mean=None, rstd=None, eps: float = 1e-5) ->
             stats.append((torch.empty(rows, dtype=torch.float32, device=dev), s))
     m32, r32 = stats[0][0], stats[1][0]
     if dev.type == "cuda":
-        with torch.cuda.device(dev):
+        with _guard(dev):
             fn = lib.hexb_layer_norm_f16 if x.dtype == torch.float16 else lib.hexb_layer_norm_f32
             _dt(x)
             check(fn(_ptr(x), _ptr(out), _ptr(weight.contiguous()), _ptr(bias.contiguous()), _ptr(m32),
@@ -118,7 +148,7 @@ def rms_norm(x, out, weight, eps: float = 1e-6) -> None:
     if weight.numel() != cols:
         raise ValueError("rms_norm: weight must have NUM_COLS elements")
     if dev.type == "cuda":
-        with torch.cuda.device(dev):
+        with _guard(dev):
             fn = lib.hexb_rms_norm_f16 if x.dtype == torch.float16 else lib.hexb_rms_norm_f32
             _dt(x)
             check(fn(_ptr(x), _ptr(out), _ptr(weight.contiguous()), rows, cols, xs, ys, float(eps),
@@ -148,7 +178,7 @@ def matmul(a, b, c, residual=None) -> None:
         if residual is not None:
             if residual.dtype != torch.float16 or residual.shape != c.shape or residual.stride(0) != c.stride(0):
                 raise ValueError("matmul: residual must be float16 with C's shape and leading dimension")
-        with torch.cuda.device(dev):
+        with _guard(dev):
             check(lib.hexb_matmul_f16(_ptr(a), _ptr(b), _ptr(c), _ptr(residual), M, N, K, lda, ldb, ldc,
                                       _dt(c), _stream(a)), "matmul")
     else:
@@ -176,7 +206,7 @@ def matmul_nt(a, bt, c, residual=None) -> None:
     if residual is not None and (residual.dtype != torch.float16 or residual.shape != c.shape
                                  or residual.stride(0) != c.stride(0)):
         raise ValueError("matmul_nt: residual must be float16 with C's shape and leading dimension")
-    with torch.cuda.device(a.device):
+    with _guard(a.device):
         check(lib.hexb_matmul_f16_nt(_ptr(a), _ptr(bt), _ptr(c), _ptr(residual), M, N, K, lda, ldb, ldc, _dt(c),
                                      _stream(a)), "matmul_nt")
 
@@ -210,7 +240,7 @@ def linear(a, w, c, bias=None, residual=None, act: str = "none", w_transposed: b
     acts = {"none": 0, "gelu_tanh": 1}
     if act not in acts:
         raise ValueError(f"linear: unknown activation {act!r}")
-    with torch.cuda.device(a.device):
+    with _guard(a.device):
         check(lib.hexb_linear_f16(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(c), M, N, K, lda, ldw, ldc,
                                   int(bool(w_transposed)), acts[act], _dt(c), _stream(a)), "linear")
 
@@ -241,7 +271,7 @@ def embedding(wte, wpe, ids, out, check_ids: bool = False) -> None:
         raise ValueError("embedding: shapes do not agree")
     if not all(t.is_contiguous() for t in (wte, wpe, ids, out)):
         raise ValueError("embedding: contiguous tensors expected")
-    with torch.cuda.device(wte.device):
+    with _guard(wte.device):
         check(lib.hexb_embedding_f16(_ptr(wte), _ptr(wpe), _ptr(ids), _ptr(out), B * S, S, Dm, V, wpe.shape[0],
                                      _stream(wte)), "embedding")
 
@@ -257,7 +287,7 @@ def matmul_swiglu(a, b_gate_up, out) -> None:
     M2, Fo, ldo = _rows2d(out, "out")
     if K != K2 or M != M2 or F2 != 2 * Fo:
         raise ValueError("matmul_swiglu: shapes do not agree")
-    with torch.cuda.device(a.device):
+    with _guard(a.device):
         check(lib.hexb_matmul_swiglu_f16(_ptr(a), _ptr(b_gate_up), _ptr(out), M, Fo, K, lda, ldb, ldo, _stream(a)),
               "matmul_swiglu")
 
@@ -265,7 +295,7 @@ def matmul_swiglu(a, b_gate_up, out) -> None:
 def hexkl_matmul_f16f16_f32(n_row, n_col, n_inner, out, act, w) -> None:
     """The HexKL runtime symbol, same argument order (bin/runtime/include/HexKLAPI.h:16-21); device tensors."""
     lib = _lib.load()
-    with torch.cuda.device(out.device):
+    with _guard(out.device):
         torch.cuda.current_stream().synchronize()  # the symbol runs on the legacy default stream
         check(lib.hexkl_matmul_f16f16_f32(n_row, n_col, n_inner, _ptr(out), _ptr(act), _ptr(w)), "hexkl_matmul")
         torch.cuda.synchronize()
@@ -294,7 +324,7 @@ def attention(q, k, v, out, sm_scale=None, causal: bool = False) -> None:
                 raise ValueError("attention: innermost stride must be 1")
             strides += [t.stride(0), t.stride(1), t.stride(2)]
         arr = (C.c_int64 * 12)(*strides)
-        with torch.cuda.device(dev):
+        with _guard(dev):
             fn = lib.hexb_attention_fwd_f16 if dt == HEXB_DT_F16 else lib.hexb_attention_fwd_f32
             check(fn(_ptr(q), _ptr(k), _ptr(v), _ptr(out), Z, H, N, D, arr, float(sm_scale), int(bool(causal)),
                      _stream(q)), "attention")
@@ -354,7 +384,7 @@ def attention_ex(q, k, v, out, mask=None, sm_scale=None, causal: bool = False) -
         d.mask_dtype = 0
     d.sm_scale = float(sm_scale)
     d.causal = int(bool(causal))
-    with torch.cuda.device(dev):
+    with _guard(dev):
         check(lib.hexb_attention_fwd_ex(C.byref(d), _stream(q)), "attention_ex")
 
 
@@ -375,7 +405,7 @@ def silu(x, out) -> None:
         raise ValueError("silu: x and out must be contiguous with equal shape and dtype")
     host = dev.type != "cuda"
     xd, od = (x.cuda(), torch.empty_like(x, device="cuda")) if host else (x, out)
-    with torch.cuda.device(xd.device):
+    with _guard(xd.device):
         fn = lib.hexb_silu_f16 if _dt(x) == HEXB_DT_F16 else lib.hexb_silu_f32
         check(fn(_ptr(xd), _ptr(od), x.numel(), _stream(xd)), "silu")
     if host:
@@ -391,7 +421,7 @@ def swiglu(gate_up, out) -> None:
         raise ValueError("swiglu: expected float16 [rows, 2*cols] -> [rows, cols]")
     if not (gate_up.is_contiguous() and out.is_contiguous()):
         raise ValueError("swiglu: tensors must be contiguous")
-    with torch.cuda.device(gate_up.device):
+    with _guard(gate_up.device):
         check(lib.hexb_swiglu_f16(_ptr(gate_up), _ptr(out), rows, cols2 // 2, _stream(gate_up)), "swiglu")
 
 
@@ -427,7 +457,7 @@ def unary(op: str, x, out) -> None:
         raise ValueError("unary: x and out must be contiguous with equal shape and dtype")
     host, (xd,) = _on_device(x)
     od = torch.empty_like(xd) if host else out
-    with torch.cuda.device(xd.device):
+    with _guard(xd.device):
         check(lib.hexb_unary(UNARY_OPS[op], _dt(x), _ptr(xd), _ptr(od), x.numel(), _stream(xd)), op)
     if host:
         out.copy_(od)
@@ -444,7 +474,7 @@ def binary(op: str, a, b, out) -> None:
         raise ValueError("binary: tensors must be contiguous")
     host, (ad, bd) = _on_device(a, b)
     od = torch.empty_like(ad) if host else out
-    with torch.cuda.device(ad.device):
+    with _guard(ad.device):
         check(lib.hexb_binary(BINARY_OPS[op], _dt(a), _ptr(ad), _ptr(bd), _ptr(od), a.numel(), _stream(ad)), op)
     if host:
         out.copy_(od)
@@ -457,7 +487,7 @@ def iota(out) -> None:
         raise ValueError("iota: contiguous tensor expected")
     host = out.device.type != "cuda"
     od = torch.empty(out.shape, dtype=out.dtype, device="cuda") if host else out
-    with torch.cuda.device(od.device):
+    with _guard(od.device):
         check(lib.hexb_iota(_dt(out), _ptr(od), out.numel(), _stream(od)), "iota")
     if host:
         out.copy_(od)
@@ -471,7 +501,7 @@ def vec_sum(x, out) -> None:
         raise ValueError("sum: out must hold one element of x's dtype, x contiguous")
     host, (xd,) = _on_device(x)
     od = torch.empty(1, dtype=x.dtype, device=xd.device) if host else out
-    with torch.cuda.device(xd.device):
+    with _guard(xd.device):
         check(lib.hexb_sum(_dt(x), _ptr(xd), _ptr(od), x.numel(), _stream(xd)), "sum")
     if host:
         out.view(-1)[:1].copy_(od)
@@ -495,7 +525,7 @@ def cumsum(x, out, axis: int = -1, reverse: bool = False) -> None:
         raise TypeError(f"cumsum: unsupported dtype {x.dtype}")
     outer = math.prod(x.shape[:axis])
     inner = math.prod(x.shape[axis + 1:])
-    with torch.cuda.device(dev):
+    with _guard(dev):
         check(lib.hexb_cumsum(dt, _ptr(x), _ptr(out), outer, x.shape[axis], inner, int(bool(reverse)), _stream(x)),
               "cumsum")
 
@@ -513,7 +543,7 @@ def rope(x, out, theta: float = 10000.0) -> None:
     B, L, H, D = x.shape
     xs = (C.c_int64 * 3)(xd.stride(0), xd.stride(1), xd.stride(2))
     os_ = (C.c_int64 * 3)(od.stride(0), od.stride(1), od.stride(2))
-    with torch.cuda.device(xd.device):
+    with _guard(xd.device):
         check(lib.hexb_rope(_dt(x), _ptr(xd), _ptr(od), B, L, H, D, xs, os_, float(theta), _stream(xd)), "rope")
     if host:
         out.copy_(od)
@@ -552,6 +582,6 @@ class DecoderStack:
             raise ValueError("decoder: float16 contiguous tensors expected")
         if x.numel() != self.cfg.batch * self.cfg.seq * self.cfg.d_model or out.numel() != x.numel():
             raise ValueError("decoder: x/out size does not match the configuration")
-        with torch.cuda.device(self.device):
+        with _guard(self.device):
             check(self.lib.hexb_decoder_forward_f16(C.byref(self.cfg), C.byref(self.cweights), _ptr(x), _ptr(out),
                                                     _ptr(self.workspace), self.ws_bytes, _stream(x)), "decoder_forward")
