@@ -992,6 +992,9 @@ int attn_device_status_fetch_and_clear(int *out) {
   HEXB_CUDA_OK(cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int)));
   if (v) HEXB_CUDA_OK(cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int)));
   if (int e = attn_pingpong_status_fetch_and_clear(&v3)) return e;
+  int v4 = 0;
+  if (int e = attn_wide_status_fetch_and_clear(&v4)) return e;
+  if (!v3) v3 = v4;
   *out = v ? v : v3;
   return HEXB_OK;
 }
@@ -1028,6 +1031,9 @@ static int attention_f16_dispatch(const void *Q, const void *K, const void *V, v
   // two score buffers / one CTA per SM
   const int which = (int)option(OPT_attn_kernel, 0);
   const bool plain = !x.mask && x.n_kv == N;
+  if (tma_ok && plain && (which == 6 || which == 7 || which == 8))   // attention_wide.cu: 2 or 4 softmax threads per row (6, 7),
+    return attn_wide_launch((const __half *)Q, (const __half *)K, (const __half *)V, Out, Z, H, N, D, s, scale_log2, causal,
+                            x.out_f32, which == 6 ? 2 : which == 7 ? 4 : 1, st);       // or two warpgroups taking turns on the blocks (8)
   if (tma_ok && plain && which == 3 && attn_pingpong_supported(Z, H, N, D, causal, di.sm_count))
     return attn_pingpong_launch((const __half *)Q, (const __half *)K, (const __half *)V, Out, Z, H, N, D, s, scale_log2,
                                 causal, x.out_f32, st);

@@ -90,6 +90,12 @@ int attn_pingpong_supported(int64_t Z, int64_t H, int64_t N, int64_t D, int caus
 int attn_pingpong_launch(const __half *Q, const __half *K, const __half *V, void *O, int64_t Z, int64_t H, int64_t N,
                          int64_t D, const int64_t *strides, float scale_log2, int causal, int out_f32, cudaStream_t st);
 int attn_pingpong_status_fetch_and_clear(int *out);
+
+// One query tile per persistent CTA, 128-key blocks, two score buffers, threads_per_row (2 or 4) softmax
+// threads per query row (attention_wide.cu).  Plain calls only.
+int attn_wide_launch(const __half *Q, const __half *K, const __half *V, void *O, int64_t Z, int64_t H, int64_t N, int64_t D,
+                     const int64_t *strides, float scale_log2, int causal, int out_f32, int threads_per_row, cudaStream_t st);
+int attn_wide_status_fetch_and_clear(int *out);
 #ifdef HEXB_ATTN_PROFILE
 unsigned long long *attn_profile_buffer();  // the buffer hexb_debug_set_attn_profile registered
 #endif
