@@ -379,8 +379,11 @@ template <typename T, int VPL, bool RMS>
 static int launch_norm_ring(const T *x, T *y, const T *w, const T *b, float *mean, float *rstd,
                             int64_t rows, int nvec, int64_t xs, int64_t ys, float inv_n, float eps,
                             int sm_count, cudaStream_t st) {
-  // rows leave as one bulk store each from a per-warp output slot (measured 44.3 -> 43.7 us on [16384 x 4096] fp16)
-  const int out_slots = option(OPT_norm_bulk_store, 1) ? 1 : 0;
+  // norm_bulk_store = 1: rows leave as one bulk store each from a per-warp output slot in shared memory.  A single
+  // short burst measured that slightly faster (44.3 -> 43.7 us on [16384 x 4096] fp16); under back-to-back replays
+  // (>= 50 ms) the lanes' own streaming stores win clearly (50.4 -> 44.2 us, RMSNorm [8192 x 2048] 14.3 -> 12.9 us),
+  // so they are the default.
+  const int out_slots = option(OPT_norm_bulk_store, 0) ? 1 : 0;
   const ring::Layout lay = ring::make_layout(nvec * 16, 0, out_slots);
   auto kern = norm_ring_kernel<T, VPL, RMS>;
   static PerDeviceOnce attr_done;
