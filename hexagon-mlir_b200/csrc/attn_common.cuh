@@ -96,6 +96,12 @@ int attn_pingpong_status_fetch_and_clear(int *out);
 int attn_wide_launch(const __half *Q, const __half *K, const __half *V, void *O, int64_t Z, int64_t H, int64_t N, int64_t D,
                      const int64_t *strides, float scale_log2, int causal, int out_f32, int threads_per_row, cudaStream_t st);
 int attn_wide_status_fetch_and_clear(int *out);
+
+// fp32 tensors on the tensor cores (kind::tf32, attention_tf32.cu): no mask; head size 64 or 128.
+int attn_tf32_supported(const void *Q, const void *K, const void *V, int64_t D, const int64_t *strides);
+int attn_tf32_launch(const float *Q, const float *K, const float *V, float *O, int64_t Z, int64_t H, int64_t N, int64_t N_KV,
+                     int64_t D, const int64_t *strides, float scale_log2, int causal, cudaStream_t st);
+int attn_tf32_status_fetch_and_clear(int *out);
 #ifdef HEXB_ATTN_PROFILE
 unsigned long long *attn_profile_buffer();  // the buffer hexb_debug_set_attn_profile registered
 #endif

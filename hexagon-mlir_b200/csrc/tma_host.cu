@@ -96,8 +96,40 @@ int encode_tmap_f16_sw128(CUtensorMap *out, const void *base, int rank, const ui
   return status;
 }
 
+static int encode_tmap_sw128_uncached(CUtensorMap *out, CUtensorMapDataType dtype, const void *base, int rank,
+                                      const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box);
+
 int encode_tmap_f16_sw128_uncached(CUtensorMap *out, const void *base, int rank, const uint64_t *dims,
                                    const uint64_t *strides_bytes, const uint32_t *box) {
+  return encode_tmap_sw128_uncached(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, base, rank, dims, strides_bytes, box);
+}
+
+// fp32 tensors of rank 2..5 (box inner extent 32 floats = 128 bytes), cached like the fp16 maps.
+int encode_tmap_f32_sw128(CUtensorMap *out, const void *base, int rank, const uint64_t *dims,
+                          const uint64_t *strides_bytes, const uint32_t *box) {
+  if (rank < 2 || rank > 5) return HEXB_ERR_BAD_ARG;
+  TmapEntry *slot = nullptr;
+  TmapKey key;
+  if (option(OPT_tmap_cache, 1)) {
+    key = make_key(base, 33, rank, dims, strides_bytes, box);
+    bool hit = false;
+    slot = tmap_cache_slot(key, &hit);
+    if (hit) {
+      *out = slot->map;
+      return HEXB_OK;
+    }
+  }
+  const int status = encode_tmap_sw128_uncached(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rank, dims, strides_bytes, box);
+  if (status == HEXB_OK && slot) {
+    slot->key = key;
+    slot->map = *out;
+    slot->valid = true;
+  }
+  return status;
+}
+
+static int encode_tmap_sw128_uncached(CUtensorMap *out, CUtensorMapDataType dtype, const void *base, int rank,
+                                      const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) {
     set_cuda_error(cudaErrorNotSupported, "cuTensorMapEncodeTiled entry point");
@@ -117,7 +149,7 @@ int encode_tmap_f16_sw128_uncached(CUtensorMap *out, const void *base, int rank,
     gs[i] = strides_bytes[i];
     if (gs[i] % 16) return HEXB_ERR_MISALIGNED;
   }
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void *>(base), gd,
+  CUresult r = fn(out, dtype, (cuuint32_t)rank, const_cast<void *>(base), gd,
                   gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {

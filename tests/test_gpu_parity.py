@@ -805,6 +805,44 @@ def test_attention_persistent_kernels_vs_oracle(dev, Z, H, N, D, causal, which):
     assert O.max_rel_err(out32.cpu(), out16.float().cpu()) < 2e-3
 
 
+@pytest.mark.parametrize("Z,H,NQ,NKV,D,causal", [
+    (1, 1, 1024, 1024, 64, False),        # the reference test's shape (scale 0.5 below)
+    (2, 3, 512, 512, 128, True), (1, 2, 300, 300, 64, True), (2, 2, 256, 640, 128, False), (1, 4, 129, 77, 64, False),
+    (1, 2, 2048, 2048, 128, True)])
+def test_attention_f32_on_tensor_cores(dev, Z, H, NQ, NKV, D, causal):
+    """fp32 tensors through the kind::tf32 kernel (forced; by default only problems of 2^30 multiply-adds and
+    more take it): the tensor cores read the operands as tf32, so the bar is the benchmark's 1e-3 relative for
+    fp32 kernels (met at unit logit spread), not the exact kernel's round-off; at the reference test's own
+    scale 0.5 on N(0, 1) inputs (logit spread 4) the tf32 scores cost up to 3e-3.  The default path at the
+    reference's test shape stays the exact kernel."""
+    g = torch.Generator().manual_seed(NQ + NKV + D)
+    q = torch.randn(Z, H, NQ, D, generator=g)
+    k, v = (torch.randn(Z, H, NKV, D, generator=g) for _ in range(2))
+    scale = 0.5 if (NQ, D) == (1024, 64) else D ** -0.5
+    ref = _sdpa_ref(q, k, v, None, scale, causal=causal and NQ == NKV)
+    out = torch.empty(Z, H, NQ, D, device=dev)
+    hexb200.set_option("attn_f32_tensor", 2)
+    try:
+        ops.attention_ex(q.to(dev), k.to(dev), v.to(dev), out, sm_scale=scale, causal=causal and NQ == NKV)
+    finally:
+        hexb200.set_option("attn_f32_tensor", 0)
+    assert hexb200.device_status() == 0
+    err_tc = O.max_rel_err(out.cpu(), ref)
+    assert err_tc < (3e-3 if scale == 0.5 else REL_F32), err_tc
+    exact = torch.empty_like(out)
+    hexb200.set_option("attn_f32_tensor", 1)
+    try:
+        ops.attention_ex(q.to(dev), k.to(dev), v.to(dev), exact, sm_scale=scale, causal=causal and NQ == NKV)
+    finally:
+        hexb200.set_option("attn_f32_tensor", 0)
+    err_exact = O.max_rel_err(exact.cpu(), ref)
+    assert err_exact < 2e-5 and err_exact < err_tc          # the CUDA-core kernel is the exact one
+    if (NQ, D) == (1024, 64):                                # what the library picks by itself at the reference's shape
+        auto = torch.empty_like(out)
+        ops.attention_ex(q.to(dev), k.to(dev), v.to(dev), auto, sm_scale=scale)
+        assert torch.equal(auto, exact)
+
+
 def test_entry_points_are_thread_safe_and_stream_ordered(dev):
     """Two host threads drive the library on their own streams at the same time (ctypes releases the GIL
     for the duration of a call); every result must equal the single-threaded one."""
