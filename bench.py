@@ -276,6 +276,9 @@ class GemmWL(Workload):
         return self.c
 
     def describe(self):
+        if (GemmWL.M, GemmWL.N, GemmWL.K) != (4096, 4096, 4096):
+            return {"workload": f"matmul fp16 {GemmWL.M} x {GemmWL.N} x {GemmWL.K} (--gemm-shape), fp32 accumulation, fp16 out",
+                    "l2": "compute-bound; the same operands every step"}
         return {"workload": "matmul fp16 4096 x 4096 x 4096, fp32 accumulation, fp16 out (configs[2])",
                 "l2": "compute-bound; operands (64 MiB) stay L2-resident between steps by design"}
 
@@ -730,8 +733,12 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads, the partitioned form and the CPU baselines")
     ap.add_argument("--eager", action="store_true", help="time K eager launches per window instead of a CUDA-graph replay of them")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement (profiling runs)")
+    ap.add_argument("--gemm-shape", default="", help="M,N,K for --workload gemm instead of 4096,4096,4096 (e.g. the decoder's "
+                                                     "down projection 8192,2048,8192)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.gemm_shape:
+        GemmWL.M, GemmWL.N, GemmWL.K = (int(v) for v in args.gemm_shape.split(","))
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
