@@ -48,7 +48,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # ncu `dram__bytes_read.sum + dram__bytes_write.sum` per launch of the dominant kernel, copied from
 # the committed summaries under profiles/ (bytes; output still dirty in L2 at kernel end is not in it).
 # The timed run does not observe these: "traffic_source" in the JSON line says so.
-NCU_TRAFFIC = {"layernorm": 216.52e6, "softmax": 33.98e6, "gemm": 87.44e6, "attention": 519.9e6, "decoder": None}
+NCU_TRAFFIC = {"layernorm": 212.33e6, "softmax": 33.98e6, "gemm": 87.44e6, "attention": 520.84e6, "decoder": None}
 
 
 def load_peaks():
