@@ -25,7 +25,7 @@ int check_launch(const char *where);  // cudaGetLastError -> status
   X(norm_ctas_per_sm) X(norm_affine_f32) X(gemm_bn) X(gemm_tail_split) X(gemm_pair) X(gemm_epi_warps) \
   X(gemm_tma_store) X(gemm_group_m) X(gemm_force_simt) X(attn_force_simt) X(attn_tiles_per_cta) X(attn_kernel)       \
   X(attn_mask_tma) X(attn_f32_tensor) X(scan_force_scalar) X(scan_segments) X(scan_kv) X(decoder_fused_swiglu)          \
-  X(host_chunks) X(pdl) X(tmap_cache) X(wait_limit_us)
+  X(host_chunks) X(host_taper) X(pdl) X(tmap_cache)
 // Descriptor-field overrides that can mis-describe an operand: compiled in only
 // with -DHEXB_DEV, absent from the shipped library's option table.
 #define HEXB_DEV_OPTIONS(X) X(gemm_b_lbo) X(gemm_b_sbo) X(attn_v_lbo) X(attn_v_sbo)
