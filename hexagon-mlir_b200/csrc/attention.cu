@@ -68,6 +68,9 @@ struct Params {
   int causal;
   int out_vec_ok;
   uint32_t v_lbo, v_sbo;
+#ifdef HEXB_DEV
+  int ablate;          // development builds: 1 = the MMA thread issues no MMAs, 2 = the softmax warps do no arithmetic
+#endif
 };
 
 template <int HD>
@@ -358,7 +361,7 @@ struct Cfg2 {
   static constexpr int Q_CHUNK = 128 * 128;           // 128 rows x 128 bytes
   static constexpr int KV_BYTES = BN * HD * 2;
   static constexpr int KV_CHUNK = BN * 128;           // 64 rows x 128 bytes
-  static constexpr int NBAR = 21;
+  static constexpr int NBAR = 25;
   static constexpr int NEEDED = Q_BYTES + 4 * KV_BYTES + NBAR * 8 + 16 + 1024;
   static constexpr int SMEM_BYTES = NEEDED < 100 * 1024 ? 100 * 1024 : NEEDED;  // caps residency at 2 CTAs/SM
   // Masked variant: one 32-row x 64-key fp16 mask tile per softmax warp, filled by TMA.  Two CTAs of
@@ -374,14 +377,28 @@ struct Cfg2 {
 
 // MASK: an additive mask tile is read by the softmax warps and the scores are formed in the base-2
 // domain as s * scale * log2(e) + mask * log2(e) before the running maximum is taken.
-template <int HD, bool MASK, int BN_ = 64>
-__global__ void __launch_bounds__(THREADS, BN_ == 64 ? 2 : 1)
+// TPR = 2: two softmax threads per query row (eight softmax warps, 320 threads): warps w and w + 4 own
+// the same 32 rows (a warp may only touch its own quarter of the TMEM lanes) and half of a block's score
+// columns and of the output columns each; they exchange their row maxima once per block, and their row
+// sums once per tile, through shared memory and a named barrier of the two warps.  Every scheduler then
+// holds two warps of a CTA that exponentiate together, which is what the special-function unit needs to
+// run at its full rate (a warp alone on its scheduler gets 8/11 of it), and the load / mask / max / pack
+// work of a block is spread over twice the threads.  Selectable (attn_kernel = 9), not the default: on
+// [4, 32, 4096, 128] it measured 583 us causal / 1048 us plain against 552 / 1000 with one thread per row.
+// Taking the kernel apart in a development build says why: with the softmax arithmetic skipped the MMAs and
+// loads alone take 92 % of the full kernel's time (with the MMAs skipped the softmax alone takes 71 %), so
+// the softmax warps are not what the kernel waits for, and the exchange only adds to their share.
+template <int HD, bool MASK, int BN_ = 64, int TPR = 1>
+__global__ void __launch_bounds__(64 + 128 * TPR, BN_ == 64 ? 2 : 1)
 attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmM,
                     const Params p) {
   using cfg = Cfg2<HD, BN_>;
   constexpr int BN = cfg::BN;
   static_assert(!MASK || BN == 64, "the masked variant stages 64-key mask tiles");
+  static_assert(TPR == 1 || (TPR == 2 && !MASK && BN == 64), "two threads per row: plain 64-key blocks only");
+  constexpr int COLS = BN / TPR;     // score columns per softmax thread
+  constexpr int OCOLS = HD / TPR;    // output columns per softmax thread
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
@@ -404,11 +421,18 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   auto v_empty = [&](uint32_t b) { return bar0 + 88 + 8 * b; };
   auto s_full = [&](uint32_t b) { return bar0 + 104 + 8 * b; };
   // barrier slots: q_full .. pv_done (5), then pairs k_full, k_empty, v_full, v_empty, s_full, p_full (12), then
-  // one m_full per softmax warp (4): NBAR = 21
+  // one m_full per softmax warp (4), one x_bar per lane quarter (4; two threads per row only): NBAR = 25
   auto p_full = [&](uint32_t b) { return bar0 + 120 + 8 * b; };
   auto m_full = [&](uint32_t w) { return bar0 + 136 + 8 * w; };   // one per softmax warp
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + 168);
+  auto x_bar = [&](uint32_t qq) { return bar0 + 168 + 8 * qq; };  // the two warps that share a lane quarter
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + cfg::NBAR * 8);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  // TPR == 2: exchange slots [parity][half][row] for row maxima and row sums (2 KiB behind the flags)
+  float *xch = reinterpret_cast<float *>(tmem_slot + 2);
+  if (TPR == 2 && pad + cfg::Q_BYTES + 4 * cfg::KV_BYTES + cfg::NBAR * 8 + 8 + 2048 > (uint32_t)cfg::SMEM_BYTES) {  // cannot happen for pad < 1024
+    if (threadIdx.x == 0) atomicExch(&g_attn_status, (int)HEXB_ERR_MISALIGNED);
+    return;
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -430,7 +454,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tc::mbar_init(q_full, 1);
     tc::mbar_init(q_empty, 1);
     tc::mbar_init(o_full, 1);
-    tc::mbar_init(o_empty, 4);
+    tc::mbar_init(o_empty, 4 * TPR);
     tc::mbar_init(pv_done, 1);
     for (uint32_t b = 0; b < 2; ++b) {
       tc::mbar_init(k_full(b), 1);
@@ -438,9 +462,10 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc::mbar_init(v_full(b), 1);
       tc::mbar_init(v_empty(b), 1);
       tc::mbar_init(s_full(b), 1);
-      tc::mbar_init(p_full(b), 4);
+      tc::mbar_init(p_full(b), 4 * TPR);
     }
     for (uint32_t w = 0; w < 4; ++w) tc::mbar_init(m_full(w), 1);
+    for (uint32_t w = 0; w < 4; ++w) tc::mbar_init(x_bar(w), 2);
     *abort_flag = 0;
     tc::fence_barrier_init();
     tc::prefetch_tensormap(&tmQ);
@@ -503,6 +528,9 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         HEXB_PROF(1)  // wait K
         tc::tc_fence_after();
         const uint32_t sK = sK0 + b * cfg::KV_BYTES;
+#ifdef HEXB_DEV
+        if (!(p.ablate & 1))
+#endif
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t qoff = (uint32_t)((k >> 2) * cfg::Q_CHUNK + (k & 3) * 32);
@@ -532,6 +560,9 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (j == 0 && t > 0 && !tc::mbar_wait(o_empty, (uint32_t)(t - 1) & 1u, abort_flag)) { ok = false; break; }
           tc::tc_fence_after();
           const uint32_t sV = sV0 + b * cfg::KV_BYTES;
+#ifdef HEXB_DEV
+          if (!(p.ablate & 1))
+#endif
 #pragma unroll
           for (int k = 0; k < BN / 16; ++k) {
             tc::mma_f16_ts(tO, tmem_base + b * BN + (uint32_t)(k * 8),
@@ -549,8 +580,25 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else {
     // ------------------------------------------------------------ softmax / correction / epilogue
     const int q = warp & 3;
+    const int hsel = TPR == 2 ? ((warp - 2) >> 2) : 0;   // which half of the columns (two threads per row)
+    const int c0 = hsel * COLS;                          // first score column of this thread inside a block
     const int r = q * 32 + lane;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    // Value exchange between the two threads of a row: slot [parity][half][row], parity alternating per
+    // exchange so that a thread never overwrites a value its partner may still have to read; the two
+    // warps meet at the mbarrier of their lane quarter (a bounded wait, like every other one here).
+    uint32_t xc = 0;
+    auto exchange = [&](float mine, float &other) -> bool {
+      float *slot = xch + (xc & 1u) * 256;
+      slot[hsel * 128 + r] = mine;
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(x_bar((uint32_t)q));
+      if (!tc::mbar_wait(x_bar((uint32_t)q), xc & 1u, abort_flag)) return false;
+      ++xc;
+      other = slot[(hsel ^ 1) * 128 + r];
+      return true;
+    };
+    (void)exchange;
     uint32_t it = 0;
     bool ok = true;
     // Mask tiles by TMA: this warp's 32 rows x 64 keys land in its own staging buffer (128-byte
@@ -582,13 +630,21 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!tc::mbar_wait(s_full(b), ph, abort_flag)) { ok = false; break; }
         HEXB_PROF(1)  // wait S
         tc::tc_fence_after();
+#ifdef HEXB_DEV
+        if (p.ablate & 2) {  // hand the block straight back
+          tc::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(p_full(b));
+          continue;
+        }
+#endif
         const uint32_t tS = tmem_base + b * BN, tP = tS;
         const int kv0 = j * BN;
         const bool need_mask = (p.causal && kv0 + BN - 1 > m0) || (kv0 + BN > p.N_KV);
-        uint32_t sv[BN];
+        uint32_t sv[COLS];
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c)
-          tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c * 32), reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
+        for (int c = 0; c < COLS / 32; ++c)
+          tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c0 + c * 32), reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
         tc::tmem_ld_wait();
         HEXB_PROF(2)  // TMEM load of S
         if constexpr (MASK) {
@@ -659,19 +715,24 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         if (need_mask) {
 #pragma unroll
-          for (int e = 0; e < BN; ++e) {
-            const int kv = kv0 + e;
+          for (int e = 0; e < COLS; ++e) {
+            const int kv = kv0 + c0 + e;
             if ((p.causal && kv > qi) || kv >= p.N_KV) sv[e] = 0xff800000u;
           }
         }
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int e = 0; e < BN; e += 8) {
+        for (int e = 0; e < COLS; e += 8) {
 #pragma unroll
           for (int u = 0; u < 4; ++u)
             mx4[u] = max3(mx4[u], __uint_as_float(sv[e + 2 * u]), __uint_as_float(sv[e + 2 * u + 1]));
         }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * (MASK ? 1.0f : p.scale_log2);
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * (MASK ? 1.0f : p.scale_log2);
+        if (TPR == 2) {  // both threads of the row end up with the same maximum
+          float other;
+          if (!exchange(mx, other)) { ok = false; break; }
+          mx = fmaxf(mx, other);
+        }
         const float m_new = fmaxf(m_ref, mx);
         if (j == 0) {
           m_ref = m_new;
@@ -683,13 +744,13 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           m_ref = m_new;
           l *= alpha;
 #pragma unroll 1
-          for (int c = 0; c < HD / 32; ++c) {
+          for (int c = 0; c < OCOLS / 32; ++c) {
             uint32_t o[32];
-            tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+            tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(hsel * OCOLS + c * 32), o);
             tc::tmem_ld_wait();
 #pragma unroll
             for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tc::tmem_st_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+            tc::tmem_st_32x32(tO + lane_off + (uint32_t)(hsel * OCOLS + c * 32), o);
           }
         }
         HEXB_PROF(3)  // mask, max, rescale
@@ -699,7 +760,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float2 mul2 = make_float2(mul, mul), neg_m2 = make_float2(neg_m, neg_m);
         float2 lacc0 = make_float2(0.f, 0.f), lacc1 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = 0; c < COLS / 32; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int e = 0; e < 32; e += 4) {
@@ -712,7 +773,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             pk[e >> 1] = pack_f16x2(pa.x, pa.y);
             pk[(e >> 1) + 1] = pack_f16x2(pb.x, pb.y);
           }
-          tc::tmem_st_32x16(tP + lane_off + (uint32_t)(c * 16), pk);
+          tc::tmem_st_32x16(tP + lane_off + (uint32_t)(c0 / 2 + c * 16), pk);
         }
         l += (lacc0.x + lacc0.y) + (lacc1.x + lacc1.y);
         HEXB_PROF(4)  // exp, pack, TMEM store issue
@@ -724,16 +785,21 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       if (!ok || !tc::mbar_wait(o_full, (uint32_t)t & 1u, abort_flag)) { ok = false; break; }
       tc::tc_fence_after();
+      if (TPR == 2) {  // the two halves of the row sum
+        float other;
+        if (!exchange(l, other)) { ok = false; break; }
+        l += other;
+      }
       const float inv = 1.0f / l;
-      const int64_t orow_off = (int64_t)z * p.so_z + (int64_t)h * p.so_h + (int64_t)qi * p.so_n;
+      const int64_t orow_off = (int64_t)z * p.so_z + (int64_t)h * p.so_h + (int64_t)qi * p.so_n + hsel * OCOLS;
       __half *orow = static_cast<__half *>(p.out) + orow_off;
       float *orow32 = static_cast<float *>(p.out) + orow_off;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < OCOLS / 32; ++c) {
         uint32_t o[32];
-        tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+        tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(hsel * OCOLS + c * 32), o);
         tc::tmem_ld_wait();
-        if (c == HD / 32 - 1) {
+        if (c == OCOLS / 32 - 1) {
           tc::tc_fence_before();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(o_empty);
@@ -902,6 +968,7 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   const int which = (int)option(OPT_attn_kernel, 0);
   const bool two_buffers = !plain || which != 1;
   const bool wide = two_buffers && !x.mask && which == 5;  // 128-key blocks, one CTA per SM
+  const bool two_per_row = two_buffers && !x.mask && which == 9;  // 64-key blocks, two softmax threads per row
   CUtensorMap tm[4];
   const __half *base[3] = {Q, K, V};
   for (int i = 0; i < 3; ++i) {
@@ -922,6 +989,8 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
                                       Cfg2<HD>::SMEM_BYTES_MASK));
     HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg2<HD, 128>::SMEM_BYTES));
+    HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, false, 64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg2<HD>::SMEM_BYTES));
     attr_done.mark(dev);
   }
   Params p;
@@ -966,6 +1035,9 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   }
   p.v_lbo = (uint32_t)HEXB_DEV_OPTION(OPT_attn_v_lbo, cfg::CHUNK_BYTES);
   p.v_sbo = (uint32_t)HEXB_DEV_OPTION(OPT_attn_v_sbo, 1024);
+#ifdef HEXB_DEV
+  p.ablate = (int)option(OPT_attn_ablate, 0);
+#endif
   // pairing pays when the tiles differ in length (causal); equal tiles run slightly faster one per CTA
   p.tiles_per_cta = (p.num_q_tiles % 2 == 0 && option(OPT_attn_tiles_per_cta, causal ? 2 : 1) == 2) ? 2 : 1;
   p.ctas_per_bh = p.num_q_tiles / p.tiles_per_cta;
@@ -973,6 +1045,9 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
   if (wide)
     launch_pdl(attn_fwd_tc2_kernel<HD, false, 128>, dim3((unsigned)ctas), dim3(THREADS), (size_t)Cfg2<HD, 128>::SMEM_BYTES, st,
+               tm[0], tm[1], tm[2], tm[3], p);
+  else if (two_per_row)
+    launch_pdl(attn_fwd_tc2_kernel<HD, false, 64, 2>, dim3((unsigned)ctas), dim3(64 + 128 * 2), (size_t)Cfg2<HD>::SMEM_BYTES, st,
                tm[0], tm[1], tm[2], tm[3], p);
   else if (two_buffers && x.mask)
     launch_pdl(attn_fwd_tc2_kernel<HD, true>, dim3((unsigned)ctas), dim3(THREADS), (size_t)Cfg2<HD>::SMEM_BYTES_MASK, st,
@@ -1045,16 +1120,17 @@ static int attention_f16_dispatch(const void *Q, const void *K, const void *V, v
                 aligned16(V);
   for (int i = 0; i < 9 && tma_ok; ++i) tma_ok = s[i] % 8 == 0 && s[i] > 0;
   // attn_kernel: 0 or 2 = 64-key blocks with two score buffers (the default), 1 = 128-key blocks / one score
-  // buffer, 3 = two query tiles per persistent CTA taking turns (attention_pingpong.cu), 5 = 128-key blocks /
-  // two score buffers / one CTA per SM
+  // buffer, 3 / 4 = two query tiles per persistent CTA taking turns with one / two softmax threads per row
+  // (attention_pingpong.cu), 5 = 128-key blocks / two score buffers / one CTA per SM, 6-8 = attention_wide.cu,
+  // 9 = the default with two softmax threads per row
   const int which = (int)option(OPT_attn_kernel, 0);
   const bool plain = !x.mask && x.n_kv == N;
   if (tma_ok && plain && (which == 6 || which == 7 || which == 8))   // attention_wide.cu: 2 or 4 softmax threads per row (6, 7),
     return attn_wide_launch((const __half *)Q, (const __half *)K, (const __half *)V, Out, Z, H, N, D, s, scale_log2, causal,
                             x.out_f32, which == 6 ? 2 : which == 7 ? 4 : 1, st);       // or two warpgroups taking turns on the blocks (8)
-  if (tma_ok && plain && which == 3 && attn_pingpong_supported(Z, H, N, D, causal, di.sm_count))
+  if (tma_ok && plain && (which == 3 || which == 4) && attn_pingpong_supported(Z, H, N, D, causal, di.sm_count))
     return attn_pingpong_launch((const __half *)Q, (const __half *)K, (const __half *)V, Out, Z, H, N, D, s, scale_log2,
-                                causal, x.out_f32, st);
+                                causal, x.out_f32, which == 4 ? 2 : 1, st);
   if (tma_ok) {
     if (D == 128)
       return attn::launch_tc<128>((const __half *)Q, (const __half *)K, (const __half *)V, Out, Z, H, N, s,

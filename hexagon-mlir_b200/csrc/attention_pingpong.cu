@@ -17,8 +17,11 @@
 //   warp 0      TMA: Q0, Q1 once per tile pair; K_j, V_j through a ring of four 128-row stages
 //   warp 1      MMA: S_t = Q_t.K_j^T (operands in shared memory), O_t += P_t.V_j (P from TMEM, V as
 //               stored); order  P0V, Q0K', P1V, Q1K', ...  so that while the softmax of tile t runs, the
-//               pipe works on the other tile
-//   warps 2-5   softmax of tile 0, warps 6-9 softmax of tile 1 (one query row per thread): tcgen05.ld
+//               pipe works on the other tile.  (One issuing thread per tile instead -- tried: the products
+//               alone then run 18 % faster, the queue in front of the pipe being only a few instructions
+//               deep, but nothing keeps the two tiles out of step any more and the whole kernel ran 25 % slower.)
+//   warps 2-5   softmax of tile 0, warps 6-9 softmax of tile 1 (one query row per thread; twice as many
+//               warps with two threads per row): tcgen05.ld
 //               the 128 scores, row max, P = exp2(S*scale - m) -> fp16 -> TMEM in two halves (the
 //               first 64 keys are handed to the MMA thread while the second 64 are exponentiated),
 //               lazy rescale of O (only when a maximum grows by more than 2^8), epilogue O/l.
@@ -38,7 +41,6 @@ using namespace attn;
 
 constexpr int BLOCK_M = 128;
 constexpr int BN = 128;
-constexpr int THREADS = 320;
 constexpr int STAGES = 4;
 
 template <int HD>
@@ -46,8 +48,9 @@ struct Cfg {
   static constexpr int CHUNKS = HD / 64;            // 64-column (128-byte) swizzle chunks
   static constexpr int TILE_BYTES = 128 * HD * 2;   // one Q tile, or one K / V stage
   static constexpr int CHUNK_BYTES = 128 * 128;     // 128 rows x 128 bytes
-  static constexpr int NBAR = 26;
-  static constexpr int SMEM_BYTES = (2 + STAGES) * TILE_BYTES + NBAR * 8 + 16 + 1024;
+  static constexpr int NBAR = 32;                   // 24 pipeline barriers + 8 exchange barriers (tile x lane quarter)
+  static constexpr int XCH_BYTES = 2 * 2 * 2 * 128 * 4;   // exchange slots [tile][parity][half][row] (two threads per row)
+  static constexpr int SMEM_BYTES = (2 + STAGES) * TILE_BYTES + NBAR * 8 + 16 + XCH_BYTES + 1024;
   static constexpr int TMEM_COLS = 512;
   static constexpr int O_COL = 256;                 // O_t at O_COL + t * 128
 };
@@ -66,10 +69,19 @@ struct Params {
   int num_items;        // work items in the launch; CTA c walks items c, c + gridDim.x, ...
   float scale_log2;
   int causal;
+#ifdef HEXB_DEV
+  int ablate;           // development builds: 1 = no MMAs are issued, 2 = the softmax warps do no arithmetic
+#endif
 };
 
-template <int HD>
-__global__ void __launch_bounds__(THREADS, 1)
+// TPR = 2: two softmax threads per query row (sixteen softmax warps, 576 threads).  Warps w and w + 4 of a
+// tile own the same 32 rows and, of every 64-key half of a block, 32 columns each (so both halves of P
+// are still handed over one after the other); they exchange row maxima once per block and row sums once
+// per tile through shared memory and an mbarrier of their own.  With one thread per row the four warps of
+// a tile sit alone on their schedulers while the other tile is in its MMA phase, and a lone warp gets
+// 8/11 of the special-function unit; the softmax of a block is in this kernel's critical chain.
+template <int HD, int TPR>
+__global__ void __launch_bounds__(64 + 256 * TPR, 1)
 attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV, const Params p) {
   using cfg = Cfg<HD>;
@@ -90,8 +102,12 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   auto o_empty = [&](int t) { return bar0 + 112 + 8u * (uint32_t)t; };
   auto kv_full = [&](uint32_t s) { return bar0 + 128 + 8u * s; };
   auto kv_empty = [&](uint32_t s) { return bar0 + 160 + 8u * s; };   // ends at bar0 + 192 = 24 barriers
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (2 + STAGES) * cfg::TILE_BYTES + 200);
+  auto x_bar = [&](int t, int qq) { return bar0 + 192 + 8u * (uint32_t)(4 * t + qq); };   // ends at bar0 + 256
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (2 + STAGES) * cfg::TILE_BYTES + cfg::NBAR * 8);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  float *xch = reinterpret_cast<float *>(tmem_slot + 4);   // 16 bytes behind the slot
+  constexpr int PART = 64 / TPR;     // score columns per thread in each 64-key half of a block
+  constexpr int OCOLS = HD / TPR;    // output columns per thread
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -119,11 +135,12 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       tc::mbar_init(q_full(t), 1);
       tc::mbar_init(q_empty(t), 1);
       tc::mbar_init(s_full(t), 1);
-      tc::mbar_init(p_full(t, 0), 4);
-      tc::mbar_init(p_full(t, 1), 4);
+      tc::mbar_init(p_full(t, 0), 4 * TPR);
+      tc::mbar_init(p_full(t, 1), 4 * TPR);
       tc::mbar_init(pv_done(t), 1);
       tc::mbar_init(o_full(t), 1);
-      tc::mbar_init(o_empty(t), 4);
+      tc::mbar_init(o_empty(t), 4 * TPR);
+      for (int qq = 0; qq < 4; ++qq) tc::mbar_init(x_bar(t, qq), 2);
     }
     for (uint32_t s = 0; s < STAGES; ++s) {
       tc::mbar_init(kv_full(s), 1);
@@ -201,6 +218,9 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       // S_t = Q_t . K^T with K in the stage of `item`
       auto issue_qk = [&](int t, uint32_t item, bool last_of_tile) {
         const uint32_t sQ = sQ0 + t * cfg::TILE_BYTES, sK = sKV0 + (item % STAGES) * cfg::TILE_BYTES;
+#ifdef HEXB_DEV
+        if (!(p.ablate & 1))
+#endif
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (uint32_t)((k >> 2) * cfg::CHUNK_BYTES + (k & 3) * 32);
@@ -246,6 +266,9 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
               if (!tc::mbar_wait(p_full(t, half), ph, abort_flag)) { ok = false; break; }
               HEXB_PROF(2 + half)  // wait P first half / second half
               tc::tc_fence_after();
+#ifdef HEXB_DEV
+              if (!(p.ablate & 1))
+#endif
 #pragma unroll
               for (int k = 4 * half; k < 4 * half + 4; ++k) {
                 // A = P rows from TMEM (16 fp16 = 8 columns per step); B = V: 16 key rows = 2 swizzle atoms
@@ -286,10 +309,24 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     }
   } else {
     // ------------------------------------------------------------ softmax / correction / epilogue
-    const int t = (warp - 2) >> 2;          // tile of this warpgroup
+    const int t = (warp - 2) / (4 * TPR);   // tile of this warpgroup
+    const int hsel = TPR == 2 ? (((warp - 2) >> 2) & 1) : 0;   // which columns of a half (two threads per row)
     const int q = warp & 3;                 // TMEM lane quarter this warp may touch
     const int r = q * 32 + lane;            // row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    // value exchange between the two threads of a row (see the kernel's head comment); bounded like every wait
+    uint32_t xc = 0;
+    auto exchange = [&](float mine, float &other) -> bool {
+      float *slot = xch + (t * 2 + (int)(xc & 1u)) * 256;
+      slot[hsel * 128 + r] = mine;
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(x_bar(t, q));
+      if (!tc::mbar_wait(x_bar(t, q), xc & 1u, abort_flag)) return false;
+      ++xc;
+      other = slot[(hsel ^ 1) * 128 + r];
+      return true;
+    };
+    (void)exchange;
     const uint32_t tS = tmem_base + (uint32_t)t * 128u, tP = tS, tO = tmem_base + cfg::O_COL + (uint32_t)t * 128u;
     uint32_t blk = 0, rounds = 0;
     bool ok = true;
@@ -309,33 +346,70 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         if (!tc::mbar_wait(s_full(t), blk & 1u, abort_flag)) { ok = false; break; }
         HEXB_PROF(1)  // wait S
         tc::tc_fence_after();
+#ifdef HEXB_DEV
+        if (p.ablate & 2) {  // hand the block straight back
+          tc::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) { tc::mbar_arrive(p_full(t, 0)); tc::mbar_arrive(p_full(t, 1)); }
+          continue;
+        }
+#endif
         const int kv0 = j * BN;
         const bool need_mask = (p.causal && kv0 + BN - 1 > m0) || (kv0 + BN > p.N_CTX);
-        uint32_t sv[BN];
+        // Element e of half h2 is key kv0 + 64 * h2 + PART * hsel + e.  One thread per row: all 128 scores
+        // stay in registers (sv[h2 * 64 + e]).  Two threads per row: 64 scores per thread do not fit the 96
+        // registers a CTA of 18 warps leaves, so the part of the second half is read for the maximum,
+        // dropped, and read again before it is exponentiated; the part of the first half stays in sv.
+        // (P of the first half lands on score columns 0..31, which both threads have read by the time
+        // they have exchanged their maxima; P of the second half on columns 32..63, likewise.)
+        uint32_t sv[TPR == 1 ? 128 : 32];
+        auto mask_part = [&](uint32_t(&v)[32], int h2, int c) {
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c)
-          tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c * 32), reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
-        tc::tmem_ld_wait();
-        HEXB_PROF(2)  // TMEM load of S
-        if (need_mask) {
-#pragma unroll
-          for (int e = 0; e < BN; ++e) {
-            const int kv = kv0 + e;
-            if ((p.causal && kv > qi) || kv >= p.N_CTX) sv[e] = 0xff800000u;  // -inf: exp2 gives 0
+          for (int e = 0; e < 32; ++e) {
+            const int kv = kv0 + 64 * h2 + PART * hsel + c * 32 + e;
+            if ((p.causal && kv > qi) || kv >= p.N_CTX) v[e] = 0xff800000u;  // -inf: exp2 gives 0
           }
-        }
-        // row maximum: three-input max, eight independent chains
+        };
         float mx8[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) mx8[u] = -INFINITY;
+        auto max_part = [&](const uint32_t(&v)[32]) {
 #pragma unroll
-        for (int e = 0; e < BN; e += 16) {
+          for (int e = 0; e < 32; e += 16)
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
-            mx8[u] = max3(mx8[u], __uint_as_float(sv[e + 2 * u]), __uint_as_float(sv[e + 2 * u + 1]));
+            for (int u = 0; u < 8; ++u) mx8[u] = max3(mx8[u], __uint_as_float(v[e + 2 * u]), __uint_as_float(v[e + 2 * u + 1]));
+        };
+        if constexpr (TPR == 1) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c * 32), reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
+          tc::tmem_ld_wait();
+          HEXB_PROF(2)  // TMEM load of S
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (need_mask) mask_part(reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]), c >> 1, c & 1);
+            max_part(reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
+          }
+        } else {
+          uint32_t second[32];
+          tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(64 + PART * hsel), second);
+          tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(PART * hsel), reinterpret_cast<uint32_t(&)[32]>(sv[0]));
+          tc::tmem_ld_wait();
+          HEXB_PROF(2)  // TMEM load of S
+          if (need_mask) {
+            mask_part(second, 1, 0);
+            mask_part(reinterpret_cast<uint32_t(&)[32]>(sv[0]), 0, 0);
+          }
+          max_part(second);
+          max_part(reinterpret_cast<uint32_t(&)[32]>(sv[0]));
         }
-        const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                               fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * p.scale_log2;
+        float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                         fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * p.scale_log2;
+        if (TPR == 2) {  // both threads of the row end up with the same maximum
+          float other;
+          if (!exchange(mx, other)) { ok = false; break; }
+          mx = fmaxf(mx, other);
+        }
         const float m_new = fmaxf(m_ref, mx);   // scale > 0: max commutes with the scaling
         if (j == 0) {
           m_ref = m_new;
@@ -347,13 +421,13 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
           m_ref = m_new;
           l *= alpha;
 #pragma unroll 1
-          for (int c = 0; c < HD / 32; ++c) {
+          for (int c = 0; c < OCOLS / 32; ++c) {
             uint32_t o[32];
-            tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+            tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(hsel * OCOLS + c * 32), o);
             tc::tmem_ld_wait();
 #pragma unroll
             for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tc::tmem_st_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+            tc::tmem_st_32x32(tO + lane_off + (uint32_t)(hsel * OCOLS + c * 32), o);
           }
           tc::tmem_st_wait();
         }
@@ -363,23 +437,35 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         const float neg_m = -m_ref;
         const float2 mul2 = make_float2(p.scale_log2, p.scale_log2), neg_m2 = make_float2(neg_m, neg_m);
         float2 lacc0 = make_float2(0.f, 0.f), lacc1 = make_float2(0.f, 0.f);
+        // 32 scores -> 32 weights: packed fp16 into 16 columns of P starting at column pcol
+        auto exp_part = [&](const uint32_t(&v)[32], uint32_t pcol) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const float2 xa = fma2(make_float2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), mul2, neg_m2);
+            const float2 xb = fma2(make_float2(__uint_as_float(v[e + 2]), __uint_as_float(v[e + 3])), mul2, neg_m2);
+            const float2 pa = make_float2(ex2_approx(xa.x), ex2_approx(xa.y));
+            const float2 pb = make_float2(ex2_approx(xb.x), ex2_approx(xb.y));
+            lacc0 = add2(lacc0, pa);
+            lacc1 = add2(lacc1, pb);
+            pk[e >> 1] = pack_f16x2(pa.x, pa.y);
+            pk[(e >> 1) + 1] = pack_f16x2(pb.x, pb.y);
+          }
+          tc::tmem_st_32x16(tP + lane_off + pcol, pk);
+        };
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
+          if constexpr (TPR == 1) {
 #pragma unroll
-          for (int c = 2 * half; c < 2 * half + 2; ++c) {
-            uint32_t pk[16];
-#pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-              const float2 xa = fma2(make_float2(__uint_as_float(sv[c * 32 + e]), __uint_as_float(sv[c * 32 + e + 1])), mul2, neg_m2);
-              const float2 xb = fma2(make_float2(__uint_as_float(sv[c * 32 + e + 2]), __uint_as_float(sv[c * 32 + e + 3])), mul2, neg_m2);
-              const float2 pa = make_float2(ex2_approx(xa.x), ex2_approx(xa.y));
-              const float2 pb = make_float2(ex2_approx(xb.x), ex2_approx(xb.y));
-              lacc0 = add2(lacc0, pa);
-              lacc1 = add2(lacc1, pb);
-              pk[e >> 1] = pack_f16x2(pa.x, pa.y);
-              pk[(e >> 1) + 1] = pack_f16x2(pb.x, pb.y);
+            for (int c = 2 * half; c < 2 * half + 2; ++c)
+              exp_part(reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]), (uint32_t)(c * 16));   // key k -> P column k / 2
+          } else {
+            if (half == 1) {  // the part of the second half comes back from TMEM
+              tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(64 + PART * hsel), reinterpret_cast<uint32_t(&)[32]>(sv[0]));
+              tc::tmem_ld_wait();
+              if (need_mask) mask_part(reinterpret_cast<uint32_t(&)[32]>(sv[0]), 1, 0);
             }
-            tc::tmem_st_32x16(tP + lane_off + (uint32_t)(c * 16), pk);
+            exp_part(reinterpret_cast<uint32_t(&)[32]>(sv[0]), (uint32_t)(32 * half + 16 * hsel));
           }
           HEXB_PROF(4)  // exp, pack, TMEM store issue
           tc::tmem_st_wait();
@@ -393,16 +479,21 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       if (!ok || !tc::mbar_wait(o_full(t), rounds & 1u, abort_flag)) { ok = false; break; }
       ++rounds;
       tc::tc_fence_after();
+      if (TPR == 2) {  // the two parts of the row sum
+        float other;
+        if (!exchange(l, other)) { ok = false; break; }
+        l += other;
+      }
       const float inv = 1.0f / l;
-      const int64_t orow_off = (int64_t)z * p.so_z + (int64_t)h * p.so_h + (int64_t)qi * p.so_n;
+      const int64_t orow_off = (int64_t)z * p.so_z + (int64_t)h * p.so_h + (int64_t)qi * p.so_n + hsel * OCOLS;
       __half *orow = static_cast<__half *>(p.out) + orow_off;
       float *orow32 = static_cast<float *>(p.out) + orow_off;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < OCOLS / 32; ++c) {
         uint32_t o[32];
-        tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(c * 32), o);
+        tc::tmem_ld_32x32(tO + lane_off + (uint32_t)(hsel * OCOLS + c * 32), o);
         tc::tmem_ld_wait();
-        if (c == HD / 32 - 1) {  // O_t is in registers: the next pair's first product may overwrite it
+        if (c == OCOLS / 32 - 1) {  // O_t is in registers: the next pair's first product may overwrite it
           tc::tc_fence_before();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(o_empty(t));
@@ -439,7 +530,7 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       HEXB_PROF(6)  // epilogue
     }
     }
-    if (threadIdx.x == 64 || threadIdx.x == 192) { HEXB_PROF_FLUSH(8 + 8 * t, 8) }
+    if (threadIdx.x == 64 || threadIdx.x == 64 + 128 * TPR) { HEXB_PROF_FLUSH(8 + 8 * t, 8) }
   }
 
   // ------------------------------------------------------------ teardown
@@ -455,7 +546,7 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_attn3_status, (int)HEXB_ERR_TIMEOUT);
 }
 
-template <int HD>
+template <int HD, int TPR>
 static int launch(const __half *Q, const __half *K, const __half *V, void *O, int64_t Z, int64_t H, int64_t N,
                   const int64_t *s, float scale_log2, int causal, int out_f32, int sm_count, cudaStream_t st) {
   using cfg = Cfg<HD>;
@@ -471,7 +562,7 @@ static int launch(const __half *Q, const __half *K, const __half *V, void *O, in
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done.is_done(dev)) {
-    HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_pingpong_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
+    HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_pingpong_kernel<HD, TPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES));
     attr_done.mark(dev);
   }
   Params p;
@@ -493,33 +584,44 @@ static int launch(const __half *Q, const __half *K, const __half *V, void *O, in
   p.ctas_per_bh = p.num_pairs / p.pairs_per_cta;
   p.scale_log2 = scale_log2;
   p.causal = causal ? 1 : 0;
+#ifdef HEXB_DEV
+  p.ablate = (int)option(OPT_attn_ablate, 0);
+#endif
   const int64_t items = (int64_t)p.ctas_per_bh * Z * H;
   if (items > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
   p.num_items = (int)items;
   const int64_t ctas = items < sm_count ? items : sm_count;   // persistent: one CTA per SM
-  launch_pdl(attn_fwd_pingpong_kernel<HD>, dim3((unsigned)ctas), dim3(THREADS), (size_t)cfg::SMEM_BYTES, st, tm[0], tm[1],
-             tm[2], p);
+  launch_pdl(attn_fwd_pingpong_kernel<HD, TPR>, dim3((unsigned)ctas), dim3(64 + 256 * TPR), (size_t)cfg::SMEM_BYTES, st, tm[0],
+             tm[1], tm[2], p);
   return check_launch("attn_pingpong");
 }
 
 }  // namespace attn3
 
-// Shapes the kernel takes (head sizes 64 and 128).  It is selectable (option attn_kernel = 3), not the
-// default: measured on B200 it runs level with the 64-key two-buffer kernel on long causal problems
-// ([4, 32, 4096, 128]: 572-580 us against 542-559 us) and behind it elsewhere -- with one score buffer per
-// tile every block pays the full Q.K^T -> softmax -> P.V hand-off chain (about 250 clocks from
-// tcgen05.commit to the waiting thread each way), which two tiles per SM do not hide.
+// Shapes the kernel takes (head sizes 64 and 128).  It is selectable (option attn_kernel = 3, or 4 for two
+// softmax threads per row), not the default: measured on B200 it runs behind the 64-key two-buffer kernel
+// ([4, 32, 4096, 128]: 597-608 us causal and 1015-1030 us plain against 543-552 and 980; with two threads
+// per row 586-592 and 1003-1018).  With one score buffer per tile a block's period is the sum of its
+// softmax, its two products and the hand-offs between them (about 250 clocks from tcgen05.commit to the
+// waiting thread each way); the exponentials of one tile cannot take less than 1024 clocks (16 per clock
+// and SM) whatever the number of threads, so the second thread per row shortens only the load / max part.
 int attn_pingpong_supported(int64_t Z, int64_t H, int64_t N, int64_t D, int causal, int sm_count) {
   (void)Z; (void)H; (void)N; (void)causal; (void)sm_count;
   return (D == 64 || D == 128) ? 1 : 0;
 }
 
 int attn_pingpong_launch(const __half *Q, const __half *K, const __half *V, void *O, int64_t Z, int64_t H, int64_t N,
-                         int64_t D, const int64_t *strides, float scale_log2, int causal, int out_f32, cudaStream_t st) {
+                         int64_t D, const int64_t *strides, float scale_log2, int causal, int out_f32, int threads_per_row,
+                         cudaStream_t st) {
   DeviceInfo di;
   if (int e = current_device(&di)) return e;
-  if (D == 128) return attn3::launch<128>(Q, K, V, O, Z, H, N, strides, scale_log2, causal, out_f32, di.sm_count, st);
-  if (D == 64) return attn3::launch<64>(Q, K, V, O, Z, H, N, strides, scale_log2, causal, out_f32, di.sm_count, st);
+#define HEXB_PP(HD_, TPR_) \
+  return attn3::launch<HD_, TPR_>(Q, K, V, O, Z, H, N, strides, scale_log2, causal, out_f32, di.sm_count, st)
+  if (D == 128 && threads_per_row == 2) HEXB_PP(128, 2);
+  if (D == 128) HEXB_PP(128, 1);
+  if (D == 64 && threads_per_row == 2) HEXB_PP(64, 2);
+  if (D == 64) HEXB_PP(64, 1);
+#undef HEXB_PP
   return HEXB_ERR_UNSUPPORTED;
 }
 

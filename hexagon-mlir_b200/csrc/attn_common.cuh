@@ -88,7 +88,8 @@ struct Extra {
 // (no additive mask, N_KV == N_CTX); returns HEXB_ERR_UNSUPPORTED for anything else.
 int attn_pingpong_supported(int64_t Z, int64_t H, int64_t N, int64_t D, int causal, int sm_count);
 int attn_pingpong_launch(const __half *Q, const __half *K, const __half *V, void *O, int64_t Z, int64_t H, int64_t N,
-                         int64_t D, const int64_t *strides, float scale_log2, int causal, int out_f32, cudaStream_t st);
+                         int64_t D, const int64_t *strides, float scale_log2, int causal, int out_f32, int threads_per_row,
+                         cudaStream_t st);
 int attn_pingpong_status_fetch_and_clear(int *out);
 
 // One query tile per persistent CTA, 128-key blocks, two score buffers, threads_per_row (2 or 4) softmax

@@ -28,7 +28,7 @@ int check_launch(const char *where);  // cudaGetLastError -> status
   X(host_chunks) X(host_taper) X(pdl) X(tmap_cache)
 // Descriptor-field overrides that can mis-describe an operand: compiled in only
 // with -DHEXB_DEV, absent from the shipped library's option table.
-#define HEXB_DEV_OPTIONS(X) X(gemm_b_lbo) X(gemm_b_sbo) X(attn_v_lbo) X(attn_v_sbo)
+#define HEXB_DEV_OPTIONS(X) X(gemm_b_lbo) X(gemm_b_sbo) X(attn_v_lbo) X(attn_v_sbo) X(attn_ablate)
 enum Opt : int {
 #define HEXB_X(n) OPT_##n,
   HEXB_OPTIONS(HEXB_X) HEXB_DEV_OPTIONS(HEXB_X)
