@@ -361,7 +361,7 @@ struct Cfg2 {
   static constexpr int Q_CHUNK = 128 * 128;           // 128 rows x 128 bytes
   static constexpr int KV_BYTES = BN * HD * 2;
   static constexpr int KV_CHUNK = BN * 128;           // 64 rows x 128 bytes
-  static constexpr int NBAR = 25;
+  static constexpr int NBAR = 27;
   static constexpr int NEEDED = Q_BYTES + 4 * KV_BYTES + NBAR * 8 + 16 + 1024;
   static constexpr int SMEM_BYTES = NEEDED < 100 * 1024 ? 100 * 1024 : NEEDED;  // caps residency at 2 CTAs/SM
   // Masked variant: one 32-row x 64-key fp16 mask tile per softmax warp, filled by TMA.  Two CTAs of
@@ -371,6 +371,10 @@ struct Cfg2 {
   static constexpr int MASK_STAGE = 32 * 128;
   static constexpr int MASK_BYTES = 4 * MASK_STAGE;
   static constexpr int SMEM_BYTES_MASK = Q_BYTES + 4 * KV_BYTES + MASK_BYTES + NBAR * 8 + 16 + 160;
+  // P through shared memory (PS form): one more 128-row x 128-byte tile; the 1024-byte alignment of the
+  // dynamic shared array is relied upon as in the masked variant (the kernel checks it)
+  static constexpr int P_BYTES = 128 * 128;
+  static constexpr int SMEM_BYTES_PS = Q_BYTES + 4 * KV_BYTES + P_BYTES + NBAR * 8 + 16 + 160;
   static constexpr int TMEM_COLS = BN == 64 ? 256 : 512;   // S0 [0,BN), S1 [BN,2BN), O [2BN,2BN+HD); P_b over S_b[0,BN/2)
   static constexpr int O_COL = 2 * BN;
 };
@@ -388,8 +392,19 @@ struct Cfg2 {
 // Taking the kernel apart in a development build says why: with the softmax arithmetic skipped the MMAs and
 // loads alone take 92 % of the full kernel's time (with the MMAs skipped the softmax alone takes 71 %), so
 // the softmax warps are not what the kernel waits for, and the exchange only adds to their share.
-template <int HD, bool MASK, int BN_ = 64, int TPR = 1>
-__global__ void __launch_bounds__(64 + 128 * TPR, BN_ == 64 ? 2 : 1)
+// PS = true ("P through shared memory"): the softmax warps write P_j as fp16 into a 16 KiB tile of shared
+// memory (128-byte swizzle, the layout of a Q chunk) and P_j.V_j reads both operands from shared memory.
+// The score buffer of block j is then free as soon as the softmax warps have loaded it, not only after
+// P_j.V_j: Q.K_{j+2}^T is issued then -- while block j is still being exponentiated -- so the scores of
+// the next block but one are under way two softmax periods before they are needed, and P_j.V_j goes out
+// the moment P_j is there instead of behind a Q.K^T.  K and V get a producer thread each (224 threads), so
+// that a K tile is not held back by the V tile queued in front of it.  Selectable (attn_kernel = 10), not the
+// default: measured on [4, 32, 4096, 128] 605 us causal / 1095 us plain against 563 / 1020 in the same process.
+// The softmax warps alone (MMAs skipped in a development build) get slower by the stores to shared memory
+// and the proxy fence (1458 against 1273 clocks per 128 x 128 block and SM), which costs more than the
+// earlier scores gain.
+template <int HD, bool MASK, int BN_ = 64, int TPR = 1, bool PS = false>
+__global__ void __launch_bounds__(64 + 128 * TPR + (PS ? 32 : 0), BN_ == 64 ? 2 : 1)
 attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmM,
                     const Params p) {
@@ -397,13 +412,15 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int BN = cfg::BN;
   static_assert(!MASK || BN == 64, "the masked variant stages 64-key mask tiles");
   static_assert(TPR == 1 || (TPR == 2 && !MASK && BN == 64), "two threads per row: plain 64-key blocks only");
+  static_assert(!PS || (TPR == 1 && !MASK && BN == 64), "P through shared memory: plain 64-key blocks, one thread per row");
   constexpr int COLS = BN / TPR;     // score columns per softmax thread
   constexpr int OCOLS = HD / TPR;    // output columns per softmax thread
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
-  constexpr uint32_t kMaskBytes = MASK ? cfg::MASK_BYTES : 0;
-  if (MASK && pad + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + cfg::NBAR * 8 + 16 > (uint32_t)cfg::SMEM_BYTES_MASK) {
+  constexpr uint32_t kMaskBytes = MASK ? cfg::MASK_BYTES : PS ? cfg::P_BYTES : 0;   // the P tile sits where the mask tiles would
+  if ((MASK && pad + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + cfg::NBAR * 8 + 16 > (uint32_t)cfg::SMEM_BYTES_MASK) ||
+      (PS && pad + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + cfg::NBAR * 8 + 16 > (uint32_t)cfg::SMEM_BYTES_PS)) {
     // the layout would not fit the allocation: every thread leaves before any barrier or TMEM use
     if (threadIdx.x == 0) atomicExch(&g_attn_status, (int)HEXB_ERR_MISALIGNED);
     return;
@@ -421,10 +438,12 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   auto v_empty = [&](uint32_t b) { return bar0 + 88 + 8 * b; };
   auto s_full = [&](uint32_t b) { return bar0 + 104 + 8 * b; };
   // barrier slots: q_full .. pv_done (5), then pairs k_full, k_empty, v_full, v_empty, s_full, p_full (12), then
-  // one m_full per softmax warp (4), one x_bar per lane quarter (4; two threads per row only): NBAR = 25
+  // one m_full per softmax warp (4), one x_bar per lane quarter (4; two threads per row only), two s_free (PS): NBAR = 27
   auto p_full = [&](uint32_t b) { return bar0 + 120 + 8 * b; };
   auto m_full = [&](uint32_t w) { return bar0 + 136 + 8 * w; };   // one per softmax warp
   auto x_bar = [&](uint32_t qq) { return bar0 + 168 + 8 * qq; };  // the two warps that share a lane quarter
+  auto s_free = [&](uint32_t b) { return bar0 + 200 + 8 * b; };   // PS: score buffer b has been loaded by the softmax warps
+  const uint32_t sP = sM0;                                        // PS: the P tile
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + cfg::NBAR * 8);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   // TPR == 2: exchange slots [parity][half][row] for row maxima and row sums (2 KiB behind the flags)
@@ -466,6 +485,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     for (uint32_t w = 0; w < 4; ++w) tc::mbar_init(m_full(w), 1);
     for (uint32_t w = 0; w < 4; ++w) tc::mbar_init(x_bar(w), 2);
+    for (uint32_t b = 0; b < 2; ++b) tc::mbar_init(s_free(b), 4);
     *abort_flag = 0;
     tc::fence_barrier_init();
     tc::prefetch_tensormap(&tmQ);
@@ -485,31 +505,39 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   pdl_wait();  // set-up done; global memory is touched from here on
   const uint32_t tO = tmem_base + cfg::O_COL;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp == 0 || (PS && warp == 6)) {
+    // ------------------------------------------------------------ TMA producer(s)
+    // One thread loads Q, K and V in turn; in the PS form warp 0 loads Q and K and warp 6 loads V.
+    const bool do_k = !PS || warp == 0, do_v = !PS || warp == 6;
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
       for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
         const int q_tile = tile_of(t);
         const int n_kv = nkv_of(q_tile);
-        if (t > 0 && !tc::mbar_wait(q_empty, (uint32_t)(t - 1) & 1u, abort_flag)) break;
-        tc::mbar_arrive_expect_tx(q_full, cfg::Q_BYTES);
+        if (do_k) {
+          if (t > 0 && !tc::mbar_wait(q_empty, (uint32_t)(t - 1) & 1u, abort_flag)) break;
+          tc::mbar_arrive_expect_tx(q_full, cfg::Q_BYTES);
 #pragma unroll
-        for (int c = 0; c < cfg::CHUNKS; ++c)
-          tc::tma_load_4d(sQ + c * cfg::Q_CHUNK, &tmQ, c * 64, q_tile * BLOCK_M, h, z, q_full);
+          for (int c = 0; c < cfg::CHUNKS; ++c)
+            tc::tma_load_4d(sQ + c * cfg::Q_CHUNK, &tmQ, c * 64, q_tile * BLOCK_M, h, z, q_full);
+        }
         for (int j = 0; j < n_kv; ++j, ++it) {
           const uint32_t b = it & 1u, ph = (it >> 1) & 1u;
-          if (!tc::mbar_wait(k_empty(b), ph ^ 1u, abort_flag)) { ok = false; break; }
-          tc::mbar_arrive_expect_tx(k_full(b), cfg::KV_BYTES);
+          if (do_k) {
+            if (!tc::mbar_wait(k_empty(b), ph ^ 1u, abort_flag)) { ok = false; break; }
+            tc::mbar_arrive_expect_tx(k_full(b), cfg::KV_BYTES);
 #pragma unroll
-          for (int c = 0; c < cfg::CHUNKS; ++c)
-            tc::tma_load_4d(sK0 + b * cfg::KV_BYTES + c * cfg::KV_CHUNK, &tmK, c * 64, j * BN, h, z, k_full(b));
-          if (!tc::mbar_wait(v_empty(b), ph ^ 1u, abort_flag)) { ok = false; break; }
-          tc::mbar_arrive_expect_tx(v_full(b), cfg::KV_BYTES);
+            for (int c = 0; c < cfg::CHUNKS; ++c)
+              tc::tma_load_4d(sK0 + b * cfg::KV_BYTES + c * cfg::KV_CHUNK, &tmK, c * 64, j * BN, h, z, k_full(b));
+          }
+          if (do_v) {
+            if (!tc::mbar_wait(v_empty(b), ph ^ 1u, abort_flag)) { ok = false; break; }
+            tc::mbar_arrive_expect_tx(v_full(b), cfg::KV_BYTES);
 #pragma unroll
-          for (int c = 0; c < cfg::CHUNKS; ++c)
-            tc::tma_load_4d(sV0 + b * cfg::KV_BYTES + c * cfg::KV_CHUNK, &tmV, c * 64, j * BN, h, z, v_full(b));
+            for (int c = 0; c < cfg::CHUNKS; ++c)
+              tc::tma_load_4d(sV0 + b * cfg::KV_BYTES + c * cfg::KV_CHUNK, &tmV, c * 64, j * BN, h, z, v_full(b));
+          }
         }
       }
     }
@@ -544,6 +572,49 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         HEXB_PROF(2)  // issue QK
       };
       uint32_t it = 0;
+      if constexpr (PS) {
+        // P.V_j: both operands from shared memory (P tile K-major like a Q chunk, V as stored)
+        constexpr uint32_t idesc_pv_ss = tc::make_idesc_f16_f32(BLOCK_M, HD, 0, 1);
+        for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
+          const int n_kv = nkv_of(tile_of(t));
+          if (!tc::mbar_wait(q_full, (uint32_t)t & 1u, abort_flag)) break;
+          // the first two score blocks of the tile; their buffers were loaded by the softmax warps two blocks ago
+          for (int j0 = 0; j0 < 2 && j0 < n_kv && ok; ++j0) {
+            const uint32_t blk = it + (uint32_t)j0;
+            if (blk >= 2 && !tc::mbar_wait(s_free(blk & 1u), ((blk >> 1) - 1u) & 1u, abort_flag)) { ok = false; break; }
+            tc::tc_fence_after();
+            issue_qk(blk, j0 + 1 == n_kv);
+          }
+          for (int j = 0; j < n_kv && ok; ++j, ++it) {
+            const uint32_t b = it & 1u, ph = (it >> 1) & 1u;
+            // scores of the next block but one go into the buffer of block j as soon as the softmax warps have
+            // that block in registers -- before P_j exists, so that P_j.V_j is not queued behind them later
+            if (j + 2 < n_kv) {
+              if (!tc::mbar_wait(s_free(b), ph, abort_flag)) { ok = false; break; }
+              tc::tc_fence_after();
+              issue_qk(it + 2u, j + 3 == n_kv);
+              if (!ok) break;
+            }
+            if (!tc::mbar_wait(p_full(0), it & 1u, abort_flag)) { ok = false; break; }
+            if (!tc::mbar_wait(v_full(b), ph, abort_flag)) { ok = false; break; }
+            if (j == 0 && t > 0 && !tc::mbar_wait(o_empty, (uint32_t)(t - 1) & 1u, abort_flag)) { ok = false; break; }
+            tc::tc_fence_after();
+            const uint32_t sV = sV0 + b * cfg::KV_BYTES;
+#ifdef HEXB_DEV
+            if (!(p.ablate & 1))
+#endif
+#pragma unroll
+            for (int k = 0; k < BN / 16; ++k) {
+              tc::mma_f16_ss(tO, tc::make_smem_desc_sw128(sP + (uint32_t)(k * 32), 16, 1024),
+                             tc::make_smem_desc_sw128(sV + (uint32_t)(k * 2048), cfg::KV_CHUNK, 1024), idesc_pv_ss,
+                             (j | k) != 0 ? 1u : 0u);
+            }
+            tc::mma_commit(v_empty(b));
+            tc::mma_commit(pv_done);
+            if (j == n_kv - 1) tc::mma_commit(o_full);
+          }
+        }
+      } else {
       for (int t = 0; t < p.tiles_per_cta && ok; ++t) {
         const int n_kv = nkv_of(tile_of(t));
         if (!tc::mbar_wait(q_full, (uint32_t)t & 1u, abort_flag)) break;
@@ -574,6 +645,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (j == n_kv - 1) tc::mma_commit(o_full);
           HEXB_PROF(5)  // issue PV
         }
+      }
       }
       HEXB_PROF_FLUSH(0, 8)
     }
@@ -634,7 +706,11 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (p.ablate & 2) {  // hand the block straight back
           tc::tc_fence_before();
           __syncwarp();
-          if (lane == 0) tc::mbar_arrive(p_full(b));
+          if (PS && it > 0 && !tc::mbar_wait(pv_done, (it - 1u) & 1u, abort_flag)) { ok = false; break; }
+          if (lane == 0) {
+            if (PS) tc::mbar_arrive(s_free(b));
+            tc::mbar_arrive(p_full(PS ? 0u : b));
+          }
           continue;
         }
 #endif
@@ -646,6 +722,11 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int c = 0; c < COLS / 32; ++c)
           tc::tmem_ld_32x32(tS + lane_off + (uint32_t)(c0 + c * 32), reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
         tc::tmem_ld_wait();
+        if constexpr (PS) {  // the scores are in registers: the buffer may take the next block but one
+          tc::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(s_free(b));
+        }
         HEXB_PROF(2)  // TMEM load of S
         if constexpr (MASK) {
           // sv <- s * scale_log2 + mask * log2(e); rows past the end read no mask
@@ -759,6 +840,9 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float mul = MASK ? 1.0f : p.scale_log2;
         const float2 mul2 = make_float2(mul, mul), neg_m2 = make_float2(neg_m, neg_m);
         float2 lacc0 = make_float2(0.f, 0.f), lacc1 = make_float2(0.f, 0.f);
+        if constexpr (PS) {  // the P tile is single: P_{it-1}.V_{it-1} must have read it
+          if (it > 0 && !tc::mbar_wait(pv_done, (it - 1u) & 1u, abort_flag)) { ok = false; break; }
+        }
 #pragma unroll
         for (int c = 0; c < COLS / 32; ++c) {
           uint32_t pk[16];
@@ -773,14 +857,32 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             pk[e >> 1] = pack_f16x2(pa.x, pa.y);
             pk[(e >> 1) + 1] = pack_f16x2(pb.x, pb.y);
           }
-          tc::tmem_st_32x16(tP + lane_off + (uint32_t)(c0 / 2 + c * 16), pk);
+          if constexpr (PS) {
+            // row r of the P tile: 128 bytes = eight 16-byte pieces, piece i stored at (i ^ (r & 7)) (128-byte swizzle)
+            const uint32_t prow = sP + (uint32_t)r * 128u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t addr = prow + ((uint32_t)((4 * c + i) ^ (r & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * i]), "r"(pk[4 * i + 1]),
+                           "r"(pk[4 * i + 2]), "r"(pk[4 * i + 3])
+                           : "memory");
+            }
+          } else {
+            tc::tmem_st_32x16(tP + lane_off + (uint32_t)(c0 / 2 + c * 16), pk);
+          }
         }
         l += (lacc0.x + lacc0.y) + (lacc1.x + lacc1.y);
         HEXB_PROF(4)  // exp, pack, TMEM store issue
+        if constexpr (PS) {
+          tc::fence_proxy_async_smem();   // the tensor pipe reads the tile through the async proxy
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(p_full(0));
+        } else {
         tc::tmem_st_wait();
         tc::tc_fence_before();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(p_full(b));
+        }
         HEXB_PROF(5)  // store wait + arrive
       }
       if (!ok || !tc::mbar_wait(o_full, (uint32_t)t & 1u, abort_flag)) { ok = false; break; }
@@ -969,6 +1071,7 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   const bool two_buffers = !plain || which != 1;
   const bool wide = two_buffers && !x.mask && which == 5;  // 128-key blocks, one CTA per SM
   const bool two_per_row = two_buffers && !x.mask && which == 9;  // 64-key blocks, two softmax threads per row
+  const bool p_smem = two_buffers && !x.mask && which == 10;      // 64-key blocks, P through shared memory
   CUtensorMap tm[4];
   const __half *base[3] = {Q, K, V};
   for (int i = 0; i < 3; ++i) {
@@ -991,6 +1094,8 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
                                       Cfg2<HD, 128>::SMEM_BYTES));
     HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, false, 64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg2<HD>::SMEM_BYTES));
+    HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, false, 64, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg2<HD>::SMEM_BYTES_PS));
     attr_done.mark(dev);
   }
   Params p;
@@ -1045,6 +1150,9 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   if (ctas > 0x7fffffffll) return HEXB_ERR_UNSUPPORTED;
   if (wide)
     launch_pdl(attn_fwd_tc2_kernel<HD, false, 128>, dim3((unsigned)ctas), dim3(THREADS), (size_t)Cfg2<HD, 128>::SMEM_BYTES, st,
+               tm[0], tm[1], tm[2], tm[3], p);
+  else if (p_smem)
+    launch_pdl(attn_fwd_tc2_kernel<HD, false, 64, 1, true>, dim3((unsigned)ctas), dim3(224), (size_t)Cfg2<HD>::SMEM_BYTES_PS, st,
                tm[0], tm[1], tm[2], tm[3], p);
   else if (two_per_row)
     launch_pdl(attn_fwd_tc2_kernel<HD, false, 64, 2>, dim3((unsigned)ctas), dim3(64 + 128 * 2), (size_t)Cfg2<HD>::SMEM_BYTES, st,
@@ -1122,7 +1230,7 @@ static int attention_f16_dispatch(const void *Q, const void *K, const void *V, v
   // attn_kernel: 0 or 2 = 64-key blocks with two score buffers (the default), 1 = 128-key blocks / one score
   // buffer, 3 / 4 = two query tiles per persistent CTA taking turns with one / two softmax threads per row
   // (attention_pingpong.cu), 5 = 128-key blocks / two score buffers / one CTA per SM, 6-8 = attention_wide.cu,
-  // 9 = the default with two softmax threads per row
+  // 9 = the default with two softmax threads per row, 10 = the default with P handed over through shared memory
   const int which = (int)option(OPT_attn_kernel, 0);
   const bool plain = !x.mask && x.n_kv == N;
   if (tma_ok && plain && (which == 6 || which == 7 || which == 8))   // attention_wide.cu: 2 or 4 softmax threads per row (6, 7),
