@@ -182,12 +182,13 @@ static void staging_drain(Staging *s) {
 // downloads from the largest piece on), so the largest piece should be as small as the per-copy
 // overhead allows.  Tapered pieces (weights 1, 2, 4, 8, ..., 8, 4, 2, 1) measured 3 % faster for the
 // matmul, whose first upload carries all of B, and 5 % slower for the row operators; host_taper = 0 / 1
-// forces one or the other.
+// forces one or the other (negative: back to the per-operator default).
 static int chunk_plan(int64_t units, int chunks, int64_t granule, int64_t *bounds, int taper_default = 0) {
   if (chunks < 1) chunks = 1;
   if (chunks > Staging::kMaxChunks) chunks = Staging::kMaxChunks;
   if (granule < 1) granule = 1;
-  const bool taper = chunks >= 4 && option(OPT_host_taper, taper_default) != 0;
+  const int tv = option(OPT_host_taper, -1);   // negative: the caller's default
+  const bool taper = chunks >= 4 && (tv < 0 ? taper_default : tv) != 0;
   int64_t w[Staging::kMaxChunks], total = 0;
   for (int i = 0; i < chunks; ++i) {
     const int edge = i < chunks - 1 - i ? i : chunks - 1 - i;

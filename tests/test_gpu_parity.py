@@ -542,6 +542,51 @@ def test_host_entry_points(dev):
     assert torch.allclose(yr, O.torch_rms_norm(xr, torch.ones(513), 1e-5), atol=1e-5)
 
 
+@pytest.mark.parametrize("chunks,taper", [(1, 0), (3, 0), (8, 0), (8, 1), (64, 1)])
+def test_host_entry_points_in_pieces(dev, chunks, taper):
+    """The `_host` entry points cut their operands into pieces that flow through upload, kernel and download
+    streams.  Rows, row blocks of A and (batch, head) pairs are independent, so whatever the number and the
+    sizes of the pieces (equal or tapered, ragged last piece, pinned or pageable memory) the result is the one
+    the device entry point gives for the whole tensor -- for the row operators to one fp16 ulp rather than bit
+    for bit, because a small piece may run the register form of the kernel where the whole matrix runs the
+    ring form, and the two sum in different orders."""
+    hexb200.set_option("host_chunks", chunks)
+    hexb200.set_option("host_taper", taper)
+    try:
+        g = torch.Generator().manual_seed(40 + chunks)
+        # LayerNorm: 4099 rows (ragged pieces), 8 MiB
+        x = torch.randn(4099, 1024, generator=g).half()
+        w, b = torch.randn(1024, generator=g).half(), torch.randn(1024, generator=g).half()
+        y_dev = torch.empty_like(x, device=dev)
+        ops.layer_norm(x.to(dev), y_dev, w.to(dev), b.to(dev))
+        for xin in (x.pin_memory(), x):
+            y, mean, rstd = torch.empty_like(x), torch.empty(4099), torch.empty(4099)
+            ops.layer_norm(xin, y, w, b, mean, rstd)
+            assert_within_ulps(y, y_dev.cpu(), 1, 0.1, 1e-3)
+            assert_within_ulps(y, O.torch_layer_norm(x, w, b, 1e-5), 1, 0.1, 1e-3)
+            assert torch.allclose(mean, x.float().mean(dim=1), atol=1e-4)
+        # matmul: 2100 rows of A (pieces are multiples of 256 rows), B whole
+        a = (torch.randn(2100, 1024, generator=g) * 0.5).half()
+        bm = (torch.randn(1024, 520, generator=g) * 0.05).half()
+        c_dev = torch.empty(2100, 520, dtype=torch.float16, device=dev)
+        ops.matmul(a.to(dev), bm.to(dev), c_dev)
+        c = torch.empty(2100, 520, dtype=torch.float16)
+        ops.matmul(a.pin_memory(), bm.pin_memory(), c)
+        assert O.max_rel_err(c, c_dev.cpu()) < 1e-3
+        assert O.max_rel_err(c, O.torch_matmul(a, bm)) < REL_F16
+        # attention: 15 (batch, head) pairs of 512 KiB each
+        q, k, v = ((torch.randn(3, 5, 2048, 128, generator=g) * 0.3).half() for _ in range(3))
+        o_dev = torch.empty_like(q, device=dev)
+        ops.attention(q.to(dev), k.to(dev), v.to(dev), o_dev, causal=True)
+        o = torch.empty_like(q)
+        ops.attention(q.pin_memory(), k.pin_memory(), v.pin_memory(), o, causal=True)
+        assert torch.equal(o, o_dev.cpu())
+        assert hexb200.device_status() == 0
+    finally:
+        hexb200.set_option("host_chunks", 8)
+        hexb200.set_option("host_taper", -1)
+
+
 def test_error_codes(dev):
     lib = hexb200.load()
     x = torch.zeros(4, 8, device=dev)
