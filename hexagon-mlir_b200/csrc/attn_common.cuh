@@ -30,8 +30,9 @@ __device__ __forceinline__ float ex2_poly(float x) {
   r = fmaf(r, f, 0.9999280571937561f);
   return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
 }
-// Measured on B200 ([4,32,4096,128] causal): 0 -> 614 us, 4 -> 649 us.  The softmax warps are
-// bound by instruction issue before the special-function unit, so the offload stays off.
+// Measured on B200 ([4,32,4096,128] causal) in the 128-key kernel: 0 -> 614 us, 4 -> 649 us; compiled into the
+// default kernel for one exponential in 32 / 16 / 8: 563 / 568 / 578 us against 563.  The special-function
+// unit is busy half of the time only, so the extra FMA-pipe instructions cost more than they free.
 constexpr int kPolyEvery = 0;  // one exponential in kPolyEvery goes through ex2_poly (0 = none)
 
 // Two fp32 lanes per instruction (sm_100 packed arithmetic): halves the issue slots of the scale-and-
