@@ -61,6 +61,18 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 }
 
 
+// (s0, s1) <- (s0, s1) * scale + the two fp16 values packed in w, in fp32: the mixed-precision add widens the
+// fp16 operand exactly, so no conversion instruction is needed
+__device__ __forceinline__ void add_mask_h2(uint32_t w, float scale, uint32_t &s0, uint32_t &s1) {
+  float2 t = fma2(make_float2(__uint_as_float(s0), __uint_as_float(s1)), make_float2(scale, scale), make_float2(0.f, 0.f));
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.f16 %0, lo, %0;\n\tadd.rn.f32.f16 %1, hi, %1;\n\t}"
+      : "+f"(t.x), "+f"(t.y)
+      : "r"(w));
+  s0 = __float_as_uint(t.x);
+  s1 = __float_as_uint(t.y);
+}
+
+
 // Phase timing for development builds (-DHEXB_ATTN_PROFILE): clock64 stamps around the phases of
 // one softmax warp and of the MMA thread of the tensor-core kernels, summed into a device buffer that
 // hexb_debug_set_attn_profile() registers.  Compiled out otherwise.
