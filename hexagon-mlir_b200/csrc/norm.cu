@@ -144,14 +144,19 @@ __device__ __forceinline__ uint32_t h2_norm_scale(uint32_t w, float rstd, uint32
   return out;
 }
 // The same two steps with the affine part in fp32 and ONE rounding at the end, as the reference's
-// fp32 expression (x - mean) * rstd * w + b rounds (test/python/triton/test_layer_norm.py:78-81).
+// fp32 expression (x - mean) * rstd * w + b rounds (test/python/triton/test_layer_norm.py:78-81).  The
+// gains and biases are widened by a mixed-precision subtract of +0 (exact, FMA pipe) rather than by
+// cvt.f32.f16, which runs on the special-function unit at 16 per clock and SM (two per element kept that
+// unit 81 % busy in the [16384 x 4096] launch); RMSNorm forms x * g exactly with the mixed-precision
+// multiply-add (the product of two fp16 values fits fp32) and applies rstd to that.
 __device__ __forceinline__ uint32_t h2_norm_affine_f32(uint32_t w, float mean, float rstd, uint32_t g, uint32_t b) {
   uint32_t out;
   asm("{\n\t.reg .b16 lo, hi, glo, ghi, blo, bhi;\n\t.reg .f32 d0, d1, g0, g1, b0, b1;\n\t"
       "mov.b32 {lo, hi}, %1;\n\tmov.b32 {glo, ghi}, %4;\n\tmov.b32 {blo, bhi}, %5;\n\t"
       "sub.rn.f32.f16 d0, lo, %2;\n\tsub.rn.f32.f16 d1, hi, %2;\n\t"
       "mul.rn.f32 d0, d0, %3;\n\tmul.rn.f32 d1, d1, %3;\n\t"
-      "cvt.f32.f16 g0, glo;\n\tcvt.f32.f16 g1, ghi;\n\tcvt.f32.f16 b0, blo;\n\tcvt.f32.f16 b1, bhi;\n\t"
+      "sub.rn.f32.f16 g0, glo, 0f00000000;\n\tsub.rn.f32.f16 g1, ghi, 0f00000000;\n\t"
+      "sub.rn.f32.f16 b0, blo, 0f00000000;\n\tsub.rn.f32.f16 b1, bhi, 0f00000000;\n\t"
       "fma.rn.f32 d0, d0, g0, b0;\n\tfma.rn.f32 d1, d1, g1, b1;\n\t"
       "cvt.rn.f16x2.f32 %0, d1, d0;\n\t}"
       : "=r"(out) : "r"(w), "f"(mean), "f"(rstd), "r"(g), "r"(b));
@@ -159,11 +164,10 @@ __device__ __forceinline__ uint32_t h2_norm_affine_f32(uint32_t w, float mean, f
 }
 __device__ __forceinline__ uint32_t h2_norm_scale_f32(uint32_t w, float rstd, uint32_t g) {
   uint32_t out;
-  asm("{\n\t.reg .b16 lo, hi, glo, ghi;\n\t.reg .f32 d0, d1, g0, g1;\n\t"
+  asm("{\n\t.reg .b16 lo, hi, glo, ghi;\n\t.reg .f32 d0, d1;\n\t"
       "mov.b32 {lo, hi}, %1;\n\tmov.b32 {glo, ghi}, %3;\n\t"
-      "cvt.f32.f16 d0, lo;\n\tcvt.f32.f16 d1, hi;\n\tcvt.f32.f16 g0, glo;\n\tcvt.f32.f16 g1, ghi;\n\t"
+      "fma.rn.f32.f16 d0, lo, glo, 0f00000000;\n\tfma.rn.f32.f16 d1, hi, ghi, 0f00000000;\n\t"
       "mul.rn.f32 d0, d0, %2;\n\tmul.rn.f32 d1, d1, %2;\n\t"
-      "mul.rn.f32 d0, d0, g0;\n\tmul.rn.f32 d1, d1, g1;\n\t"
       "cvt.rn.f16x2.f32 %0, d1, d0;\n\t}"
       : "=r"(out) : "r"(w), "f"(rstd), "r"(g));
   return out;
