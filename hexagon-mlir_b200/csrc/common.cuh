@@ -131,13 +131,19 @@ template <>
 struct Vec16<__half> {
   static constexpr int N = 8;
   uint4 raw;
+  // fp16 -> fp32 by the mixed-precision subtract of +0 (sm_100: sub.rn.f32.f16, exact for every input, -0
+  // included): it runs on the FMA pipe at 128 lanes per clock and SM, where cvt.f32.f16 shares the
+  // 16-lane unit of the transcendentals and made the fp16 forms of the streaming kernels conversion-bound.
+  static __device__ __forceinline__ void widen2(uint32_t w, float &lo, float &hi) {
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tsub.rn.f32.f16 %0, l, 0f00000000;\n\tsub.rn.f32.f16 %1, h, 0f00000000;\n\t}"
+        : "=f"(lo), "=f"(hi)
+        : "r"(w));
+  }
   __device__ __forceinline__ void unpack(float (&f)[8]) const {
-    const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 t = __half22float2(h[i]);
-      f[2 * i] = t.x; f[2 * i + 1] = t.y;
-    }
+    widen2(raw.x, f[0], f[1]);
+    widen2(raw.y, f[2], f[3]);
+    widen2(raw.z, f[4], f[5]);
+    widen2(raw.w, f[6], f[7]);
   }
   __device__ __forceinline__ void pack(const float (&f)[8]) {
     __half2 *h = reinterpret_cast<__half2 *>(&raw);
@@ -146,9 +152,22 @@ struct Vec16<__half> {
   }
 };
 
+// tanh by the special-function unit's own instruction: one operation per value, max relative error 2^-11
+// (half an fp16 ulp), against two (ex2 + rcp) for the exponential form.  Used where the result is rounded
+// to fp16 anyway.
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
-template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) {
+  float f;
+  asm("sub.rn.f32.f16 %0, %1, 0f00000000;" : "=f"(f) : "h"(__half_as_ushort(v)));
+  return f;
+}
 template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }

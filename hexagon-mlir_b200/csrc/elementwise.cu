@@ -9,6 +9,11 @@
 namespace hexb {
 
 __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }  // 2 ulp
+// fp16 data: x * sigmoid(x) = x/2 * (1 + tanh(x/2)) with the one-instruction tanh (2^-11), see tanh_approx
+__device__ __forceinline__ float silu_h(float x) {
+  const float hx = 0.5f * x;
+  return fmaf(hx, tanh_approx(hx), hx);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256) silu_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t n,
@@ -24,11 +29,12 @@ __global__ void __launch_bounds__(256) silu_kernel(const T *__restrict__ x, T *_
     float f[E];
     a.unpack(f);
 #pragma unroll
-    for (int e = 0; e < E; ++e) f[e] = silu_f(f[e]);
+    for (int e = 0; e < E; ++e) f[e] = sizeof(T) == 2 ? silu_h(f[e]) : silu_f(f[e]);
     a.pack(f);
     st_stream_as<Raw>(y + v * E, a.raw);
   }
-  for (int64_t i = nvec * E + tid; i < n; i += nth) y[i] = from_f32<T>(silu_f(to_f32<T>(x[i])));
+  for (int64_t i = nvec * E + tid; i < n; i += nth)
+    y[i] = from_f32<T>(sizeof(T) == 2 ? silu_h(to_f32<T>(x[i])) : silu_f(to_f32<T>(x[i])));
 }
 
 // out[r, c] = silu(gu[r, c]) * gu[r, cols + c]; cols % 8 == 0.
