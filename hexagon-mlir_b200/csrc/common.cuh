@@ -22,7 +22,7 @@ int check_launch(const char *where);  // cudaGetLastError -> status
 #define HEXB_OPTIONS(X)                                                                              \
   X(softmax_vpt_max) X(softmax_force_stream) X(softmax_ring) X(softmax_bulk_store) X(norm_ring)      \
   X(norm_bulk_store) X(ring_bytes_per_warp) X(ring_map) X(norm_vpt_max) X(norm_force_stream)         \
-  X(norm_ctas_per_sm) X(norm_affine_f32) X(gemm_bn) X(gemm_tail_split) X(gemm_pair) X(gemm_epi_warps) \
+  X(norm_ctas_per_sm) X(norm_affine_f32) X(gemm_bn) X(gemm_tail_split) X(gemm_pair) X(gemm_pair_min_tiles) X(gemm_epi_warps) \
   X(gemm_tma_store) X(gemm_group_m) X(gemm_force_simt) X(attn_force_simt) X(attn_tiles_per_cta) X(attn_kernel)       \
   X(attn_mask_tma) X(attn_f32_tensor) X(scan_force_scalar) X(scan_segments) X(scan_kv) X(decoder_fused_swiglu)          \
   X(host_chunks) X(host_taper) X(pdl) X(tmap_cache)

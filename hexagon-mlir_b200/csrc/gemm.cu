@@ -890,9 +890,14 @@ static int matmul_impl(const __half *A, const __half *B, OutT *C, const __half *
     if (N <= 64 || (int64_t)tiles_m * ((N + 127) / 128) < di.sm_count / 2) bn = 64;
     else if (N <= 128 || (int64_t)tiles_m * ((N + 255) / 256) < di.sm_count) bn = 128;
   }
-  // CTA-pair kernel for problems with at least one 256 x 256 tile per pair of SMs
+  // CTA-pair kernel from 256 x 256 tiles for 27 % of the SMs on (40 tiles on 148 SMs).  Below a full wave
+  // the alternative is 128 x 128 tiles on every SM, which fetch twice the operand bytes per FLOP through L2
+  // and are bound by that: [1024 x 4096 x 4096] 39.7 us on 256 single-CTA tiles against 27.3 us on 64 pair
+  // tiles, [768 x 4096 x 4096] 39.2 against 25.6; with 32 pair tiles ([512 x 4096 x 4096], [1024 x 2048 x
+  // 2048]) the idle SMs weigh more and the single-CTA kernel stays 8-15 % ahead.
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
-  if (option(OPT_gemm_bn, 0) == 0 && option(OPT_gemm_pair, 1) && pair_tiles >= di.sm_count / 2)
+  if (option(OPT_gemm_bn, 0) == 0 && option(OPT_gemm_pair, 1) &&
+      pair_tiles >= option(OPT_gemm_pair_min_tiles, (di.sm_count * 27 + 99) / 100))
     return launch_tc_pair<OutT, EPI, BT>(epi, sm, tmA, tmB, C, R, (int)M, (int)N, (int)K, ldc, ldr, vec_ok, di.sm_count, di.l2_bytes, st);
   if (BT && bn == 64) bn = 128;  // the transposed form loads Bt in 128-row boxes
   switch (bn) {
