@@ -850,6 +850,24 @@ def test_attention_persistent_kernels_vs_oracle(dev, Z, H, N, D, causal, which):
     assert O.max_rel_err(out32.cpu(), out16.float().cpu()) < 2e-3
 
 
+@pytest.mark.parametrize("tiles_per_cta", [1, 2])
+@pytest.mark.parametrize("Z,H,N,D", [(2, 3, 1024, 128), (1, 2, 512, 64), (1, 1, 2048, 128), (1, 5, 300, 128)])
+def test_attention_causal_tile_pairing(dev, Z, H, N, D, tiles_per_cta):
+    """Causal calls walk one query tile per CTA or a long and a short one; the library pairs them only when the
+    pairs cover the SMs, so both forms are forced here on shapes of either kind (an odd tile count falls
+    back to one tile per CTA by itself) and held to the oracle."""
+    q, k, v = O.make_attention_inputs(Z, H, N, D)
+    ref = O.torch_attention(q, k, v, D ** -0.5, True)
+    out = torch.empty_like(q, device=dev)
+    hexb200.set_option("attn_tiles_per_cta", tiles_per_cta)
+    try:
+        ops.attention(q.to(dev), k.to(dev), v.to(dev), out, causal=True)
+    finally:
+        hexb200.set_option("attn_tiles_per_cta", 0)
+    assert hexb200.device_status() == 0
+    assert O.max_rel_err(out.cpu(), ref) < REL_F16
+
+
 @pytest.mark.parametrize("Z,H,NQ,NKV,D,causal", [
     (1, 1, 1024, 1024, 64, False),        # the reference test's shape (scale 0.5 below)
     (2, 3, 512, 512, 128, True), (1, 2, 300, 300, 64, True), (2, 2, 256, 640, 128, False), (1, 4, 129, 77, 64, False),
