@@ -274,7 +274,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const float x0 = fmaf(__uint_as_float(sv[c * 32 + e]), p.scale_log2, neg_m);
             const float x1 = fmaf(__uint_as_float(sv[c * 32 + e + 1]), p.scale_log2, neg_m);
             const float p0 = ex2_approx(x0);
-            const float p1 = (kPolyEvery > 0 && ((e + 1) % kPolyEvery) == kPolyEvery - 1) ? ex2_poly(x1) : ex2_approx(x1);
+            const float p1 = ex2_approx(x1);
             l0 += p0;
             l1 += p1;
             pk[e >> 1] = pack_f16x2(p0, p1);

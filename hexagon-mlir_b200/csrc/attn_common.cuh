@@ -19,8 +19,10 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 // 2^x on the FMA pipe: x = n + f with n = round(x) taken from the mantissa of x + 1.5*2^23,
 // 2^f by a degree-3 polynomial on [-0.5, 0.5] (max relative error 7.5e-5, below the fp16 rounding
-// of P), exponent patched in with an integer add.  Used for a fraction of the exponentials so the
-// special-function unit is not the only path they go through.
+// of P), exponent patched in with an integer add.  Kept for reference, not called: routing one exponential
+// in 4 through it measured 614 -> 649 us in the 128-key kernel ([4,32,4096,128] causal), and one in
+// 32 / 16 / 8 in the default kernel 563 / 568 / 578 us against 563.  The special-function unit is busy
+// half of the time only, so the extra FMA-pipe instructions cost more than they free.
 __device__ __forceinline__ float ex2_poly(float x) {
   x = fmaxf(x, -126.0f);
   const float t = x + 12582912.0f;
@@ -30,10 +32,6 @@ __device__ __forceinline__ float ex2_poly(float x) {
   r = fmaf(r, f, 0.9999280571937561f);
   return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
 }
-// Measured on B200 ([4,32,4096,128] causal) in the 128-key kernel: 0 -> 614 us, 4 -> 649 us; compiled into the
-// default kernel for one exponential in 32 / 16 / 8: 563 / 568 / 578 us against 563.  The special-function
-// unit is busy half of the time only, so the extra FMA-pipe instructions cost more than they free.
-constexpr int kPolyEvery = 0;  // one exponential in kPolyEvery goes through ex2_poly (0 = none)
 
 // Two fp32 lanes per instruction (sm_100 packed arithmetic): halves the issue slots of the scale-and-
 // shift and of the row-sum in the softmax loop, which is bound by instruction issue.
