@@ -361,7 +361,7 @@ struct Cfg2 {
   static constexpr int Q_CHUNK = 128 * 128;           // 128 rows x 128 bytes
   static constexpr int KV_BYTES = BN * HD * 2;
   static constexpr int KV_CHUNK = BN * 128;           // 64 rows x 128 bytes
-  static constexpr int NBAR = 27;
+  static constexpr int NBAR = 29;
   static constexpr int NEEDED = Q_BYTES + 4 * KV_BYTES + NBAR * 8 + 16 + 1024;
   static constexpr int SMEM_BYTES = NEEDED < 100 * 1024 ? 100 * 1024 : NEEDED;  // caps residency at 2 CTAs/SM
   // Masked variant: one 32-row x 64-key fp16 mask tile per softmax warp, filled by TMA.  Two CTAs of
@@ -403,7 +403,11 @@ struct Cfg2 {
 // The softmax warps alone (MMAs skipped in a development build) get slower by the stores to shared memory
 // and the proxy fence (1458 against 1273 clocks per 128 x 128 block and SM), which costs more than the
 // earlier scores gain.
-template <int HD, bool MASK, int BN_ = 64, int TPR = 1, bool PS = false>
+// K3 = true: a third K stage (in the 16 KiB the mask tiles or the P tile would take), so that the K tile of
+// block j + 2 can be fetched while blocks j and j + 1 are both still unread.  Selectable (attn_kernel = 11);
+// it measured level with two stages (551 / 1001 us against 551 / 1000 on [4, 32, 4096, 128] causal / plain):
+// the K tiles are not what the MMA thread waits for.
+template <int HD, bool MASK, int BN_ = 64, int TPR = 1, bool PS = false, bool K3 = false>
 __global__ void __launch_bounds__(64 + 128 * TPR + (PS ? 32 : 0), BN_ == 64 ? 2 : 1)
 attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmM,
@@ -413,14 +417,15 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   static_assert(!MASK || BN == 64, "the masked variant stages 64-key mask tiles");
   static_assert(TPR == 1 || (TPR == 2 && !MASK && BN == 64), "two threads per row: plain 64-key blocks only");
   static_assert(!PS || (TPR == 1 && !MASK && BN == 64), "P through shared memory: plain 64-key blocks, one thread per row");
+  static_assert(!K3 || (TPR == 1 && !MASK && !PS && BN == 64), "third K stage: the plain 64-key kernel only");
   constexpr int COLS = BN / TPR;     // score columns per softmax thread
   constexpr int OCOLS = HD / TPR;    // output columns per softmax thread
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw_addr = tc::smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
-  constexpr uint32_t kMaskBytes = MASK ? cfg::MASK_BYTES : PS ? cfg::P_BYTES : 0;   // the P tile sits where the mask tiles would
+  constexpr uint32_t kMaskBytes = MASK ? cfg::MASK_BYTES : (PS || K3) ? cfg::P_BYTES : 0;   // the P tile or the third K stage sits where the mask tiles would
   if ((MASK && pad + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + cfg::NBAR * 8 + 16 > (uint32_t)cfg::SMEM_BYTES_MASK) ||
-      (PS && pad + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + cfg::NBAR * 8 + 16 > (uint32_t)cfg::SMEM_BYTES_PS)) {
+      ((PS || K3) && pad + cfg::Q_BYTES + 4 * cfg::KV_BYTES + kMaskBytes + cfg::NBAR * 8 + 16 > (uint32_t)cfg::SMEM_BYTES_PS)) {
     // the layout would not fit the allocation: every thread leaves before any barrier or TMEM use
     if (threadIdx.x == 0) atomicExch(&g_attn_status, (int)HEXB_ERR_MISALIGNED);
     return;
@@ -432,13 +437,19 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t sM0 = sV0 + 2 * cfg::KV_BYTES;   // mask tiles (masked variant only)
   const uint32_t bar0 = sM0 + kMaskBytes;
   const uint32_t q_full = bar0, q_empty = bar0 + 8, o_full = bar0 + 16, o_empty = bar0 + 24, pv_done = bar0 + 32;
-  auto k_full = [&](uint32_t b) { return bar0 + 40 + 8 * b; };
-  auto k_empty = [&](uint32_t b) { return bar0 + 56 + 8 * b; };
+  auto k_full = [&](uint32_t b) { return b < 2 ? bar0 + 40 + 8 * b : bar0 + 216; };    // b == 2: third K stage (K3)
+  auto k_empty = [&](uint32_t b) { return b < 2 ? bar0 + 56 + 8 * b : bar0 + 224; };
+  auto k_stage = [&](uint32_t b) { return b < 2 ? sQ + cfg::Q_BYTES + b * cfg::KV_BYTES : sQ + cfg::Q_BYTES + 4 * cfg::KV_BYTES; };
+  // K stage and phase of block `blk`: two stages alternate with the score buffers, three have their own count
+  auto k_slot = [&](uint32_t blk, uint32_t &kb, uint32_t &kph) {
+    if (K3) { kb = blk % 3u; kph = (blk / 3u) & 1u; }
+    else { kb = blk & 1u; kph = (blk >> 1) & 1u; }
+  };
   auto v_full = [&](uint32_t b) { return bar0 + 72 + 8 * b; };
   auto v_empty = [&](uint32_t b) { return bar0 + 88 + 8 * b; };
   auto s_full = [&](uint32_t b) { return bar0 + 104 + 8 * b; };
   // barrier slots: q_full .. pv_done (5), then pairs k_full, k_empty, v_full, v_empty, s_full, p_full (12), then
-  // one m_full per softmax warp (4), one x_bar per lane quarter (4; two threads per row only), two s_free (PS): NBAR = 27
+  // one m_full per softmax warp (4), one x_bar per lane quarter (4; two threads per row only), two s_free (PS), k_full / k_empty of the third K stage (K3): NBAR = 29
   auto p_full = [&](uint32_t b) { return bar0 + 120 + 8 * b; };
   auto m_full = [&](uint32_t w) { return bar0 + 136 + 8 * w; };   // one per softmax warp
   auto x_bar = [&](uint32_t qq) { return bar0 + 168 + 8 * qq; };  // the two warps that share a lane quarter
@@ -486,6 +497,8 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (uint32_t w = 0; w < 4; ++w) tc::mbar_init(m_full(w), 1);
     for (uint32_t w = 0; w < 4; ++w) tc::mbar_init(x_bar(w), 2);
     for (uint32_t b = 0; b < 2; ++b) tc::mbar_init(s_free(b), 4);
+    tc::mbar_init(k_full(2), 1);
+    tc::mbar_init(k_empty(2), 1);
     *abort_flag = 0;
     tc::fence_barrier_init();
     tc::prefetch_tensormap(&tmQ);
@@ -525,11 +538,13 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int j = 0; j < n_kv; ++j, ++it) {
           const uint32_t b = it & 1u, ph = (it >> 1) & 1u;
           if (do_k) {
-            if (!tc::mbar_wait(k_empty(b), ph ^ 1u, abort_flag)) { ok = false; break; }
-            tc::mbar_arrive_expect_tx(k_full(b), cfg::KV_BYTES);
+            uint32_t kb, kph;
+            k_slot(it, kb, kph);
+            if (!tc::mbar_wait(k_empty(kb), kph ^ 1u, abort_flag)) { ok = false; break; }
+            tc::mbar_arrive_expect_tx(k_full(kb), cfg::KV_BYTES);
 #pragma unroll
             for (int c = 0; c < cfg::CHUNKS; ++c)
-              tc::tma_load_4d(sK0 + b * cfg::KV_BYTES + c * cfg::KV_CHUNK, &tmK, c * 64, j * BN, h, z, k_full(b));
+              tc::tma_load_4d(k_stage(kb) + c * cfg::KV_CHUNK, &tmK, c * 64, j * BN, h, z, k_full(kb));
           }
           if (do_v) {
             if (!tc::mbar_wait(v_empty(b), ph ^ 1u, abort_flag)) { ok = false; break; }
@@ -550,12 +565,14 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // S_{blk} = Q . K_{blk}^T into score buffer blk % 2
       HEXB_PROF_DECL(8)
       auto issue_qk = [&](uint32_t blk, bool last_of_tile) {
-        const uint32_t b = blk & 1u, ph = (blk >> 1) & 1u;
+        const uint32_t b = blk & 1u;
+        uint32_t kb, kph;
+        k_slot(blk, kb, kph);
         HEXB_PROF(0)  // other
-        if (!tc::mbar_wait(k_full(b), ph, abort_flag)) { ok = false; return; }
+        if (!tc::mbar_wait(k_full(kb), kph, abort_flag)) { ok = false; return; }
         HEXB_PROF(1)  // wait K
         tc::tc_fence_after();
-        const uint32_t sK = sK0 + b * cfg::KV_BYTES;
+        const uint32_t sK = k_stage(kb);
 #ifdef HEXB_DEV
         if (!(p.ablate & 1))
 #endif
@@ -567,7 +584,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                          tc::make_smem_desc_sw128(sK + koff, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
         }
         tc::mma_commit(s_full(b));
-        tc::mma_commit(k_empty(b));
+        tc::mma_commit(k_empty(kb));
         if (last_of_tile) tc::mma_commit(q_empty);
         HEXB_PROF(2)  // issue QK
       };
@@ -1073,6 +1090,7 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   const bool wide = two_buffers && !x.mask && which == 5;  // 128-key blocks, one CTA per SM
   const bool two_per_row = two_buffers && !x.mask && which == 9;  // 64-key blocks, two softmax threads per row
   const bool p_smem = two_buffers && !x.mask && which == 10;      // 64-key blocks, P through shared memory
+  const bool k3 = two_buffers && !x.mask && which == 11;          // 64-key blocks, three K stages
   CUtensorMap tm[4];
   const __half *base[3] = {Q, K, V};
   for (int i = 0; i < 3; ++i) {
@@ -1097,6 +1115,8 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
                                       Cfg2<HD>::SMEM_BYTES));
     HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, false, 64, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg2<HD>::SMEM_BYTES_PS));
+    HEXB_CUDA_OK(cudaFuncSetAttribute(attn_fwd_tc2_kernel<HD, false, 64, 1, false, true>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2<HD>::SMEM_BYTES_PS));
     attr_done.mark(dev);
   }
   Params p;
@@ -1162,6 +1182,9 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   if (wide)
     launch_pdl(attn_fwd_tc2_kernel<HD, false, 128>, dim3((unsigned)ctas), dim3(THREADS), (size_t)Cfg2<HD, 128>::SMEM_BYTES, st,
                tm[0], tm[1], tm[2], tm[3], p);
+  else if (k3)
+    launch_pdl(attn_fwd_tc2_kernel<HD, false, 64, 1, false, true>, dim3((unsigned)ctas), dim3(THREADS), (size_t)Cfg2<HD>::SMEM_BYTES_PS,
+               st, tm[0], tm[1], tm[2], tm[3], p);
   else if (p_smem)
     launch_pdl(attn_fwd_tc2_kernel<HD, false, 64, 1, true>, dim3((unsigned)ctas), dim3(224), (size_t)Cfg2<HD>::SMEM_BYTES_PS, st,
                tm[0], tm[1], tm[2], tm[3], p);
@@ -1241,7 +1264,8 @@ static int attention_f16_dispatch(const void *Q, const void *K, const void *V, v
   // attn_kernel: 0 or 2 = 64-key blocks with two score buffers (the default), 1 = 128-key blocks / one score
   // buffer, 3 / 4 = two query tiles per persistent CTA taking turns with one / two softmax threads per row
   // (attention_pingpong.cu), 5 = 128-key blocks / two score buffers / one CTA per SM, 6-8 = attention_wide.cu,
-  // 9 = the default with two softmax threads per row, 10 = the default with P handed over through shared memory
+  // 9 = the default with two softmax threads per row, 10 = the default with P handed over through shared memory,
+  // 11 = the default with three K stages
   const int which = (int)option(OPT_attn_kernel, 0);
   const bool plain = !x.mask && x.n_kv == N;
   if (tma_ok && plain && (which == 6 || which == 7 || which == 8))   // attention_wide.cu: 2 or 4 softmax threads per row (6, 7),

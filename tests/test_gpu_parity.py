@@ -801,12 +801,12 @@ def test_attention_masked_f32_and_odd_head_dim(dev):
     assert O.max_rel_err(out.cpu(), _sdpa_ref(q.half(), k.half(), v.half(), mask.half(), 1.0 / math.sqrt(D))) < REL_F16
 
 
-@pytest.mark.parametrize("which", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10])
+@pytest.mark.parametrize("which", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11])
 @pytest.mark.parametrize("causal", [False, True])
 def test_attention_selectable_kernels_agree_with_default(dev, which, causal):
     """Every tensor-core kernel stays selectable -- 128-key single-buffer (1), 64-key two-buffer (2), two
     query tiles per CTA with one (3) or two (4) softmax threads per row, 128-key two-buffer (5), 128-key two-buffer with two (6) or four (7) softmax
-    threads per row, two warpgroups taking turns (8), 64-key two-buffer with two threads per row (9) or with P handed over through shared memory (10) -- and must give the result of the kernel the library picks by itself, to rounding, on
+    threads per row, two warpgroups taking turns (8), 64-key two-buffer with two threads per row (9) or with P handed over through shared memory (10) or with three K stages (11) -- and must give the result of the kernel the library picks by itself, to rounding, on
     full, ragged and odd-tile-count shapes."""
     for Z, H, N, D in [(1, 2, 512, 128), (2, 1, 300, 64), (1, 1, 640, 128)]:
         g = torch.Generator().manual_seed(N + D + which)
@@ -825,7 +825,7 @@ def test_attention_selectable_kernels_agree_with_default(dev, which, causal):
 @pytest.mark.parametrize("Z,H,N,D,causal", [
     (2, 3, 1024, 128, True), (2, 3, 1024, 128, False), (1, 4, 1000, 64, True), (1, 2, 129, 128, True),
     (3, 2, 384, 64, False), (1, 1, 2048, 128, True), (1, 2, 100, 128, False), (1, 1, 257, 64, True)])
-@pytest.mark.parametrize("which", [3, 4, 6, 7, 8, 9, 10])
+@pytest.mark.parametrize("which", [3, 4, 6, 7, 8, 9, 10, 11])
 def test_attention_persistent_kernels_vs_oracle(dev, Z, H, N, D, causal, which):
     """The kernels that exchange values between softmax warps or walk several tiles (forced: two query
     tiles per CTA = 3, 4, several softmax threads per row = 4, 6, 7, 9, alternating warpgroups = 8) against the oracle: even and odd tile counts, ragged lengths, a tile that lies wholly past the last
