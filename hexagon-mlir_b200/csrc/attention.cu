@@ -60,6 +60,7 @@ struct Params {
   int mask_vec_ok;     // 16-byte loads of the mask row are aligned
   int mask_tma;        // the mask arrives through the tensor map (fp16, 16-byte aligned strides, one row per query)
   int mask_h_on, mask_z_on;   // 0: that dimension of the mask is broadcast (its tensor-map extent is 1)
+  int head_major;             // CTA order: the batches of a head adjacent (mask shared by them), else the heads of a batch
   int64_t sm_z, sm_h, sm_q;
   int num_q_tiles;
   int tiles_per_cta;   // query tiles one CTA walks (1 or 2)
@@ -468,7 +469,10 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int lane = threadIdx.x & 31;
   const int bh = blockIdx.x / p.ctas_per_bh;
   const int q_rank = blockIdx.x - bh * p.ctas_per_bh;
-  const int z = bh / p.H, h = bh - z * p.H;
+  // (batch, head) of this CTA: batch-major by default; head-major when a mask is shared by the batches of a
+  // head, so that the CTAs which read the same mask tiles run next to each other and find them in L2
+  const int z = p.head_major ? bh % p.Z : bh / p.H;
+  const int h = p.head_major ? bh / p.Z : bh - z * p.H;
   const int kv_blocks = (p.N_KV + BN - 1) / BN;
   auto tile_of = [&](int t) {
     if (p.causal) return t == 0 ? p.num_q_tiles - 1 - q_rank : q_rank;
@@ -1137,6 +1141,7 @@ static int launch_tc(const __half *Q, const __half *K, const __half *V, void *O,
   }
   p.mask_h_on = x.sm[1] != 0;
   p.mask_z_on = x.sm[0] != 0;
+  p.head_major = (x.mask && p.mask_h_on && !p.mask_z_on && Z > 1) ? 1 : 0;
   p.mask_tma = p.mask_vec_ok && !x.mask_f32 && x.sm[2] >= x.n_kv && option(OPT_attn_mask_tma, 1);
   tm[3] = tm[0];
   if (p.mask_tma) {

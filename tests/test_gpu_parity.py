@@ -704,6 +704,23 @@ def test_attention_masked_f16(dev, Z, H, NQ, NKV, D, mask_dtype, out_dtype):
     assert hexb200.device_status() == 0
 
 
+@pytest.mark.parametrize("mask_dtype", [torch.float16, torch.float32])
+def test_attention_mask_shared_by_the_batches_of_a_head(dev, mask_dtype):
+    """A mask of shape [1, H, N_Q, N_KV] broadcast over the batch: the kernel then orders its CTAs head-major
+    (the batches of a head next to each other, so that they find the head's mask tiles in L2); the (batch,
+    head) a CTA works on must still be the right one."""
+    g = torch.Generator().manual_seed(91)
+    Z, H, NQ, NKV, D = 3, 5, 256, 320, 128
+    q = torch.randn(Z, H, NQ, D, generator=g).half()
+    k, v = (torch.randn(Z, H, NKV, D, generator=g).half() for _ in range(2))
+    mask = torch.randn(1, H, NQ, NKV, generator=g).to(mask_dtype)
+    out = torch.empty(Z, H, NQ, D, dtype=torch.float16, device=dev)
+    ops.attention_ex(q.to(dev), k.to(dev), v.to(dev), out, mask=mask.to(dev).expand(Z, H, NQ, NKV))
+    ref = _sdpa_ref(q, k, v, mask.expand(Z, H, NQ, NKV), 1.0 / math.sqrt(D))
+    assert O.max_rel_err(out.cpu(), ref) < REL_F16
+    assert hexb200.device_status() == 0
+
+
 def test_attention_masked_matches_oracle_rank3(dev):
     """tm_tensor.attention form: rank-3 operands, mask [batch, seq_q, seq_kv], checked against the C oracle."""
     g = torch.Generator().manual_seed(77)
