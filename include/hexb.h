@@ -270,7 +270,11 @@ int hexb_decoder_forward_f16_noalloc(const hexb_decoder_config *cfg, const hexb_
 /* ---- host-buffer entry points (the launcher path).  Replace the generated wrapper main() that
  * loads `<kernel>_t{i}.raw`, runs the kernel and dumps `<kernel>_o{i}.raw`
  * (qcom_hexagon_backend/backend/triton_hexagon_launcher.py:111-123,
- *  backend/hexagon_launcher_base.py:430-437): tensors cross the host/device boundary inside. */
+ *  backend/hexagon_launcher_base.py:430-437): tensors cross the host/device boundary inside.
+ * Tensors are contiguous and row-major.  Rows, 256-row blocks of A and (batch, head) pairs are cut into
+ * pieces (option "host_chunks", default 8) whose upload, kernel and download overlap on three streams;
+ * the overlap needs page-locked host memory (cudaHostAlloc / cudaHostRegister), pageable memory gives
+ * the same result with the pieces one after the other.  One call at a time per process (a lock). */
 int hexb_softmax_host(int dtype, const void *x, void *y, int64_t rows, int64_t cols);
 int hexb_layer_norm_host(int dtype, const void *x, void *y, const void *weight, const void *bias,
                          float *mean, float *rstd, int64_t rows, int64_t cols, float eps);
